@@ -72,6 +72,9 @@ def _register_builtin() -> None:
     from ..models.vokusun import VokusunConfig, vokusun_plan
 
     register_architecture(["Vokusun", "vokusun"], VokusunConfig.from_dict, vokusun_plan)
+    from ..models.lozanex import LozanexConfig, lozanex_plan
+
+    register_architecture(["Lozanex", "lozanex"], LozanexConfig.from_dict, lozanex_plan)
 
 
 _register_builtin()

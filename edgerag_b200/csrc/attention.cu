@@ -8,7 +8,8 @@
 // sequence lives in page block_table[seq][p / page_size] at offset p % page_size.  Keys are
 // stored already rotated.  A query at position p sees keys max(0, p - window + 1) .. p
 // (window <= 0: all keys 0 .. p) and, with a window, also the keys 0 .. keep_first - 1 whatever their
-// distance.  Query head h reads kv head h / (nq / nkv).
+// distance.  A negative `window` stands for a mask of chunks: the query sees the keys from the start of its own run of
+// -window positions (runs counted from position 0 of the sequence) up to itself.  Query head h reads kv head h / (nq / nkv).
 //
 // Both kernels give every thread its own keys and its own online-softmax state (running max,
 // denominator, float accumulator of D values), so the inner loop has no cross-thread traffic;
@@ -133,7 +134,7 @@ attention_rows_kernel(const T* __restrict__ q, int q_row_stride, const T* __rest
   const int seq = seq_of_token[t], pos = positions[t];
   const int kvh = h / (nq / nkv);
   const int* bt = block_tables + (size_t)seq * max_pages;
-  const int k_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int k_lo = first_visible_key(pos, window);
 
   LaneState<D> st;
   st.init();
@@ -185,7 +186,7 @@ attention_decode_split_kernel(const T* __restrict__ q, int q_row_stride, const T
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = token_of_seq[seq];
   const int pos = positions[t];
-  const int k_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int k_lo = first_visible_key(pos, window);
   // Splits are aligned to multiples of split_keys in absolute key positions.
   const int first_split = k_lo / split_keys;
   const int begin = max(k_lo, (first_split + split) * split_keys);
@@ -260,7 +261,7 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_a
   const int h = blockIdx.x, seq = blockIdx.y;
   const int t = token_of_seq[seq];
   const int pos = positions[t];
-  const int k_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int k_lo = first_visible_key(pos, window);
   // never beyond what the split kernel's grid wrote (a caller that understates max_splits gets the
   // first max_splits splits merged, not its neighbours' scratch)
   const int n_splits = min(pos / split_keys - k_lo / split_keys + 1, max_splits);

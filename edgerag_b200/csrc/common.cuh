@@ -164,6 +164,14 @@ __device__ __forceinline__ void rotate_pair(float a, float b, float cs, float sn
   hi = __fmaf_rn(b, cs, __fmul_rn(a, sn));
 }
 
+// The first key a query at position `pos` sees.  `window` > 0: the last `window` keys; `window` < 0: the keys of the
+// query's own chunk, chunks being runs of -window positions counted from position 0 of the sequence; 0: every key.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+  if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+  if (window < 0) return pos - pos % (-window);
+  return 0;
+}
+
 // Chained launches.  Kernels that run back to back in the decode step are launched with
 // programmatic stream serialization: the next kernel's blocks may be scheduled while the previous
 // kernel drains, which hides the launch latency between the many short kernels of a step.  Every

@@ -1320,3 +1320,214 @@ ERB_EXPORT int erb_qk_prepare(void* qkv, int ld, const float* q_bias, const floa
                  slots, (elem_t*)k_pages, (elem_t*)v_pages, n_tokens, nq, nkv, head_dim, page_size, values_are_keys);
   return check_launch("qk_prepare");
 }
+
+// ---------------------------------------------------------------------------------------------
+// The residual add between RMS norms, for blocks whose sublayers read the stream itself and norm what they add:
+//   h = hidden[row]                                   float
+//   h = h * rsqrt(mean(h^2) + self_eps) * self_w      when self_w is given (the stream normed in place: after the embedding)
+//   d = delta[row] (rows of T, or `n_parts` float arrays added in order and rounded to T once) (+ bias, in float)
+//   d = d * rsqrt(mean(d^2) + post_eps) * post_w      when post_w is given (the norm that closes the sublayer; stays float)
+//   h += d, stored back when `write_back`
+//   out[o] = round_T(h)                               when w is null
+//          = round_T(h * rsqrt(mean(h^2) + eps) * w)  otherwise
+// Every mean, scale and sum is float; eps sits inside the root.  One block per row, the row parked in shared memory.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_between_kernel(float* __restrict__ hidden, const T* __restrict__ delta, const float* __restrict__ parts, int n_parts,
+                   size_t part_stride, const float* __restrict__ bias, const float* __restrict__ self_w, float self_eps,
+                   const float* __restrict__ post_w, float post_eps, const float* __restrict__ w, float eps,
+                   T* __restrict__ out, int out_ld, const int* __restrict__ rows, int width, int write_back) {
+  chain_wait();
+  extern __shared__ float rb_smem[];     // width floats for the row, width for the update, 32 of scratch
+  float* row = rb_smem;
+  float* upd = rb_smem + width;
+  float* scratch = upd + width;
+  const int o = blockIdx.x;
+  const int r = rows ? rows[o] : o;
+  float* h = hidden + (size_t)r * width;
+  const float inv_w = 1.f / (float)width;
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = h[i];
+    row[i] = v;
+    sq += v * v;
+  }
+  if (self_w) {
+    const float rs = rsqrtf(block_sum(sq, scratch) * inv_w + self_eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = row[i] * rs * self_w[i];
+  }
+  const T* d = delta ? delta + (size_t)r * width : nullptr;
+  const float* ps = parts ? parts + (size_t)r * width : nullptr;
+  if (d || ps) {
+    float dsq = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float v;
+      if (d) {
+        v = Elem<T>::load(d + i);
+      } else {
+        v = ps[i];
+        for (int sp = 1; sp < n_parts; ++sp) v += ps[sp * part_stride + i];
+        v = Elem<T>::round(v);
+      }
+      if (bias) v += bias[i];
+      upd[i] = v;
+      dsq += v * v;
+    }
+    float rs = 1.f;
+    if (post_w) rs = rsqrtf(block_sum(dsq, scratch) * inv_w + post_eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+      row[i] += post_w ? upd[i] * rs * post_w[i] : upd[i];
+  }
+  if (write_back && (self_w || d || ps))
+    for (int i = threadIdx.x; i < width; i += blockDim.x) h[i] = row[i];
+  if (!out) return;
+  T* y = out + (size_t)o * out_ld;
+  if (!w) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) Elem<T>::store(y + i, row[i]);
+    return;
+  }
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) s2 += row[i] * row[i];
+  const float rs = rsqrtf(block_sum(s2, scratch) * inv_w + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) Elem<T>::store(y + i, row[i] * rs * w[i]);
+}
+
+ERB_EXPORT int erb_rms_between(void* hidden, const void* delta, int n_parts, long long part_stride, const float* bias,
+                               const float* self_w, float self_eps, const float* post_w, float post_eps, const float* w,
+                               float eps, void* out, int out_ld, const int* rows, int n_rows, int width, int write_back,
+                               void* stream) {
+  if (n_rows <= 0) return ERB_OK;
+  if (width <= 0 || (out && out_ld < width)) return fail(ERB_ERR_ARG, "rms_between: bad sizes");
+  const size_t smem = sizeof(float) * (2 * (size_t)width + 32);
+  if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "rms_between: rows of %d entries", width);
+  auto kern = rms_between_kernel<elem_t>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "rms_between: %s", cudaGetErrorString(e));
+  }
+  const bool in_parts = n_parts > 0;
+  launch_chained(kern, dim3(n_rows), dim3(width >= 1024 ? 256 : 128), smem, (cudaStream_t)stream, (float*)hidden,
+                 in_parts ? nullptr : (const elem_t*)delta, in_parts ? (const float*)delta : nullptr, n_parts,
+                 (size_t)part_stride, bias, self_w, self_eps, post_w, post_eps, w, eps, (elem_t*)out, out_ld, rows, width,
+                 write_back);
+  return check_launch("rms_between");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Float rows plus one vector: y[t, i] += vec[i] (a bias after a product whose result stayed float).
+// ---------------------------------------------------------------------------------------------
+__global__ void bias_rows_kernel(float* __restrict__ y, const float* __restrict__ vec, int width, size_t total) {
+  chain_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < total) y[idx] += vec[idx % width];
+}
+
+ERB_EXPORT int erb_bias_rows(float* y, const float* vec, int n_rows, int width, void* stream) {
+  if (n_rows <= 0) return ERB_OK;
+  const size_t total = (size_t)n_rows * width;
+  launch_chained(bias_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, y, vec, width, total);
+  return check_launch("bias_rows");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Queries, keys and values of a token made ready for attention where the norm of queries and keys runs over the whole
+// projection (all heads of the token at once).  A row is [q: nq heads | k: nkv heads | v: nkv heads], every head D
+// entries wide; D may be wider than the true head sizes (the entries beyond them hold zeros and their biases and norm
+// weights are zero), so the means divide by the true counts `q_count` and `k_count`.
+//   q = row_q + q_bias;  q = q * rsqrt(sum(q^2) / q_count + eps) * q_norm[all entries]      float
+//   k likewise with k_bias, k_count, k_norm;   v = row_v + v_bias
+//   the first rot_dim entries of every q and k head are turned, entry i with entry i + rot_dim / 2, by position * inv_freq[i]
+//   q goes back in place, k and v to the token's cache slot (page * page_size + offset; negative or no pages: not written).
+// `has_kv` 0: the row holds queries only (a layer that reads another layer's keys and values).
+// One block per token.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+qkv_whole_norm_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                      const float* __restrict__ v_bias, const float* __restrict__ q_norm, const float* __restrict__ k_norm,
+                      float q_count, float k_count, float eps, const int* __restrict__ positions,
+                      const float* __restrict__ inv_freq, int rot_dim, const int* __restrict__ slots, T* __restrict__ k_pages,
+                      T* __restrict__ v_pages, int nq, int nkv, int D, int page_size, int has_kv) {
+  chain_wait();
+  extern __shared__ float wn_smem[];      // (nq + nkv) * D floats, then 32 of scratch
+  const int qw = nq * D, kw = has_kv ? nkv * D : 0;
+  float* q_s = wn_smem;
+  float* k_s = wn_smem + qw;
+  float* scratch = k_s + kw;
+  const int t = blockIdx.x;
+  T* row = qkv + (size_t)t * ld;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < qw; i += blockDim.x) {
+    const float v = Elem<T>::load(row + i) + (q_bias ? q_bias[i] : 0.f);
+    q_s[i] = v;
+    sq += v * v;
+  }
+  for (int i = threadIdx.x; i < kw; i += blockDim.x) {
+    const float v = Elem<T>::load(row + qw + i) + (k_bias ? k_bias[i] : 0.f);
+    k_s[i] = v;
+    sk += v * v;
+  }
+  const float rq = q_norm ? rsqrtf(block_sum(sq, scratch) / q_count + eps) : 1.f;
+  const float rk = (has_kv && k_norm) ? rsqrtf(block_sum(sk, scratch) / k_count + eps) : 1.f;
+  __syncthreads();
+  const int pos = positions[t];
+  const int half = rot_dim / 2;
+  const int slot = (has_kv && slots && k_pages) ? slots[t] : -1;
+  const int page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot % page_size : 0;
+  // every thread owns entries (head, i) with i < D - half: i < half is a turned pair (i, i + half), the others pass
+  const int per_head = D - half;
+  for (int idx = threadIdx.x; idx < (nq + (has_kv ? nkv : 0)) * per_head; idx += blockDim.x) {
+    const int head = idx / per_head, j = idx % per_head;
+    const bool is_q = head < nq;
+    const int hh = is_q ? head : head - nq;
+    const float* src = is_q ? q_s + hh * D : k_s + hh * D;
+    const float* nw = is_q ? (q_norm ? q_norm + hh * D : nullptr) : (k_norm ? k_norm + hh * D : nullptr);
+    const float rs = is_q ? rq : rk;
+    T* dst = is_q ? row + hh * D
+                  : (slot >= 0 ? k_pages + (((size_t)page * nkv + hh) * page_size + offset) * D : nullptr);
+    if (!dst) continue;
+    if (j < half) {
+      const float a = src[j] * rs * (nw ? nw[j] : 1.f), b = src[j + half] * rs * (nw ? nw[j + half] : 1.f);
+      float sn, cs;
+      sincosf((float)pos * inv_freq[j], &sn, &cs);
+      float lo, hi;
+      rotate_pair(a, b, cs, sn, lo, hi);
+      Elem<T>::store(dst + j, lo);
+      Elem<T>::store(dst + j + half, hi);
+    } else {
+      const int i = j + half;
+      Elem<T>::store(dst + i, src[i] * rs * (nw ? nw[i] : 1.f));
+    }
+  }
+  if (slot >= 0 && v_pages) {
+    for (int i = threadIdx.x; i < kw; i += blockDim.x) {
+      const int hh = i / D, e = i % D;
+      const float v = Elem<T>::load(row + qw + kw + i) + (v_bias ? v_bias[i] : 0.f);
+      Elem<T>::store(v_pages + (((size_t)page * nkv + hh) * page_size + offset) * D + e, v);
+    }
+  }
+}
+
+ERB_EXPORT int erb_qkv_whole_norm(void* qkv, int ld, const float* q_bias, const float* k_bias, const float* v_bias,
+                                  const float* q_norm, const float* k_norm, int q_count, int k_count, float eps,
+                                  const int* positions, const float* inv_freq, int rot_dim, const int* slots, void* k_pages,
+                                  void* v_pages, int n_tokens, int nq, int nkv, int head_dim, int page_size, int has_kv,
+                                  void* stream) {
+  if (n_tokens <= 0) return ERB_OK;
+  if (nq <= 0 || nkv <= 0 || head_dim <= 0 || rot_dim < 0 || rot_dim % 2 || rot_dim > head_dim || (rot_dim && !inv_freq) ||
+      q_count <= 0 || k_count <= 0 || page_size <= 0)
+    return fail(ERB_ERR_ARG, "qkv_whole_norm: bad sizes (rot_dim %d of head_dim %d)", rot_dim, head_dim);
+  if (ld < (nq + (has_kv ? 2 * nkv : 0)) * head_dim) return fail(ERB_ERR_ARG, "qkv_whole_norm: rows too narrow");
+  const size_t smem = sizeof(float) * ((size_t)(nq + (has_kv ? nkv : 0)) * head_dim + 32);
+  if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "qkv_whole_norm: %d heads of %d", nq + nkv, head_dim);
+  auto kern = qkv_whole_norm_kernel<elem_t>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "qkv_whole_norm: %s", cudaGetErrorString(e));
+  }
+  launch_chained(kern, dim3(n_tokens), dim3(256), smem, (cudaStream_t)stream, (elem_t*)qkv, ld, q_bias, k_bias, v_bias, q_norm,
+                 k_norm, (float)q_count, (float)k_count, eps, positions, inv_freq, rot_dim, slots, (elem_t*)k_pages,
+                 (elem_t*)v_pages, nq, nkv, head_dim, page_size, has_kv);
+  return check_launch("qkv_whole_norm");
+}

@@ -1,0 +1,255 @@
+// A feed-forward of routed experts over a ragged batch, without a host round trip: every launch has a shape that
+// depends on the number of tokens only, and the kernels find their work in lists made on the device.
+//
+//   1. route:   z = W_router x (float), s = sigmoid(z); the `top` experts with the largest z (the lower index wins a tie);
+//               per token the chosen experts and their scores s.  A (token, choice) is a "pair", numbered token * top + choice.
+//   2. lists:   count the pairs of every expert, make the offsets (and the offsets in row tiles), write the pair numbers of
+//               every expert in rising order behind its offset.
+//   3. gate/up: for every expert the rows of its pairs, each row the token's input times the pair's score (rounded to T
+//               once), times [W_gate; W_up]^T; act = silu(gate) * up, stored in the order of the lists.
+//   4. down:    act times W_down^T, stored as float at [choice][token][:]: the partial sums of the tokens' updates, which
+//               whoever adds the update sums in the order of the choices.
+// The products walk k in one fixed order whatever tile a row falls into, so a token's result does not depend on the
+// other tokens of the step.  Accumulation is float; T is the type of the operands.
+#include "common.cuh"
+
+using namespace erb;
+
+ERB_DEFINE_LAST_ERROR(erb_last_error)
+
+namespace {
+
+constexpr int kRouteThreads = 128;
+
+// One block per token.  Shared memory: n_experts floats.
+template <typename T>
+__global__ void __launch_bounds__(kRouteThreads)
+moe_route_kernel(const T* __restrict__ x, int ld, const float* __restrict__ w_router, int width, int n_experts, int top,
+                 int* __restrict__ choice, float* __restrict__ score) {
+  chain_wait();
+  extern __shared__ float z_s[];
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const T* row = x + (size_t)t * ld;
+  for (int e = warp; e < n_experts; e += kRouteThreads / 32) {
+    const float* w = w_router + (size_t)e * width;
+    float acc = 0.f;
+    for (int k = lane; k < width; k += 32) acc = fmaf(Elem<T>::load(row + k), w[k], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z_s[e] = acc;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  for (int c = 0; c < top; ++c) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < n_experts; e += 32) {
+      const float z = z_s[e];
+      if (z > best) { best = z; arg = e; }       // rising e within a lane: the first maximum stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (lane == 0) {
+      choice[(size_t)t * top + c] = arg;
+      score[(size_t)t * top + c] = 1.f / (1.f + expf(-best));
+      z_s[arg] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+// One block per expert: how many pairs chose it.
+__global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ choice, int n_pairs, int* __restrict__ counts) {
+  chain_wait();
+  __shared__ float scratch[32];
+  const int e = blockIdx.x;
+  int c = 0;
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) c += choice[i] == e;
+  const float total = block_sum((float)c, scratch);      // (exact: counts stay far below 2^24)
+  if (threadIdx.x == 0) counts[e] = (int)total;
+}
+
+// One block: offsets[e] = pairs of the experts before e; tiles[e] = row tiles (of `tile_rows`) of the experts before e.
+__global__ void moe_offsets_kernel(const int* __restrict__ counts, int n_experts, int tile_rows, int* __restrict__ offsets,
+                                   int* __restrict__ tiles) {
+  chain_wait();
+  if (threadIdx.x != 0) return;
+  int off = 0, tl = 0;
+  for (int e = 0; e < n_experts; ++e) {
+    offsets[e] = off;
+    tiles[e] = tl;
+    off += counts[e];
+    tl += (counts[e] + tile_rows - 1) / tile_rows;
+  }
+  offsets[n_experts] = off;
+  tiles[n_experts] = tl;
+}
+
+// One block per expert: its pairs, in rising order, behind its offset.
+__global__ void __launch_bounds__(256) moe_fill_kernel(const int* __restrict__ choice, int n_pairs, const int* __restrict__ offsets,
+                                                       int* __restrict__ order) {
+  chain_wait();
+  __shared__ int warp_counts[8];
+  __shared__ int base_s;
+  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) base_s = offsets[e];
+  __syncthreads();
+  for (int i0 = 0; i0 < n_pairs; i0 += 256) {
+    const int i = i0 + threadIdx.x;
+    const bool mine = i < n_pairs && choice[i] == e;
+    const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+    if (lane == 0) warp_counts[warp] = __popc(ballot);
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_counts[w];
+    if (mine) order[base_s + before + __popc(ballot & ((1u << lane) - 1))] = i;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int all = 0;
+      for (int w = 0; w < 8; ++w) all += warp_counts[w];
+      base_s += all;
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The experts' products on CUDA cores: a block owns TM rows of one expert's list and TN columns; k is walked in
+// steps of BK in rising order with one float accumulator per output.
+//   GATED: rows are gathered and scaled inputs, the weight holds `n_out` gate rows followed by `n_out` up rows, the
+//          output is silu(gate) * up in T at the row's place in the list;
+//   else:  rows are the list's rows of `a`, the output is float at [choice][token][:].
+// ---------------------------------------------------------------------------------------------
+constexpr int kTM = 32, kTN = 64, kBK = 32;
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_product_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weights, const int* __restrict__ offsets,
+                   const int* __restrict__ tiles, const int* __restrict__ order, const float* __restrict__ score, int n_experts,
+                   int top, int n_tokens, int n_out, int k_dim, T* __restrict__ act, float* __restrict__ parts) {
+  chain_wait();
+  __shared__ float a_s[kTM][kBK + 1];
+  __shared__ float b_s[kTN][kBK + 1];
+  __shared__ float b2_s[GATED ? kTN : 1][kBK + 1];
+  __shared__ int pair_s[kTM];
+  __shared__ float scale_s[kTM];
+  const int tile = blockIdx.x;
+  if (tile >= tiles[n_experts]) return;
+  int e = 0;
+  {
+    int lo = 0, hi = n_experts;                          // the last e with tiles[e] <= tile
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (tiles[mid] <= tile) lo = mid; else hi = mid;
+    }
+    e = lo;
+  }
+  const int row0 = offsets[e] + (tile - tiles[e]) * kTM;
+  const int n_rows = min(kTM, offsets[e + 1] - row0);
+  const int col0 = blockIdx.y * kTN;
+  if (threadIdx.x < kTM) {
+    const int r = threadIdx.x;
+    const int pair = r < n_rows ? order[row0 + r] : -1;
+    pair_s[r] = pair;
+    scale_s[r] = (GATED && pair >= 0) ? score[pair] : 1.f;
+  }
+  __syncthreads();
+  const T* w = weights + (size_t)e * (GATED ? 2 : 1) * n_out * k_dim;
+  const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;   // rows 2 ty, 2 ty + 1; columns tx + 16 j
+  float acc[2][4] = {}, acc2[2][4] = {};
+  for (int k0 = 0; k0 < k_dim; k0 += kBK) {
+    for (int idx = threadIdx.x; idx < kTM * kBK; idx += 256) {
+      const int r = idx / kBK, kk = idx % kBK;
+      float v = 0.f;
+      if (r < n_rows && k0 + kk < k_dim) {
+        if (GATED) v = Elem<T>::round(scale_s[r] * Elem<T>::load(a + (size_t)(pair_s[r] / top) * lda + k0 + kk));
+        else v = Elem<T>::load(a + (size_t)(row0 + r) * lda + k0 + kk);
+      }
+      a_s[r][kk] = v;
+    }
+    for (int idx = threadIdx.x; idx < kTN * kBK; idx += 256) {
+      const int c = idx / kBK, kk = idx % kBK;
+      const bool ok = col0 + c < n_out && k0 + kk < k_dim;
+      b_s[c][kk] = ok ? Elem<T>::load(w + (size_t)(col0 + c) * k_dim + k0 + kk) : 0.f;
+      if (GATED) b2_s[c][kk] = ok ? Elem<T>::load(w + (size_t)(n_out + col0 + c) * k_dim + k0 + kk) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < kBK; ++kk) {
+      const float a0 = a_s[2 * ty][kk], a1 = a_s[2 * ty + 1][kk];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float b = b_s[tx + 16 * j][kk];
+        acc[0][j] = fmaf(a0, b, acc[0][j]);
+        acc[1][j] = fmaf(a1, b, acc[1][j]);
+        if (GATED) {
+          const float b2 = b2_s[tx + 16 * j][kk];
+          acc2[0][j] = fmaf(a0, b2, acc2[0][j]);
+          acc2[1][j] = fmaf(a1, b2, acc2[1][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = 2 * ty + i;
+    if (r >= n_rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = col0 + tx + 16 * j;
+      if (c >= n_out) continue;
+      if (GATED) {
+        Elem<T>::store(act + (size_t)(row0 + r) * n_out + c, silu_mul(acc[i][j], acc2[i][j]));
+      } else {
+        const int pair = pair_s[r];
+        parts[((size_t)(pair % top) * n_tokens + pair / top) * n_out + c] = acc[i][j];
+      }
+    }
+  }
+}
+
+}  // namespace
+
+ERB_EXPORT int erb_moe_tile_rows() { return kTM; }
+
+ERB_EXPORT int erb_moe_route(const void* x, int ld, const float* w_router, int n_tokens, int width, int n_experts, int top,
+                             int* choice, float* score, int* counts, int* offsets, int* tiles, int* order, void* stream) {
+  if (n_tokens <= 0) return ERB_OK;
+  if (width <= 0 || n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 8192)
+    return fail(ERB_ERR_ARG, "moe_route: %d of %d experts", top, n_experts);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int n_pairs = n_tokens * top;
+  launch_chained(moe_route_kernel<elem_t>, dim3(n_tokens), dim3(kRouteThreads), sizeof(float) * n_experts, s, (const elem_t*)x, ld,
+                 w_router, width, n_experts, top, choice, score);
+  int rc = check_launch("moe_route");
+  if (rc) return rc;
+  launch_chained(moe_count_kernel, dim3(n_experts), dim3(256), 0, s, (const int*)choice, n_pairs, counts);
+  if ((rc = check_launch("moe_count"))) return rc;
+  launch_chained(moe_offsets_kernel, dim3(1), dim3(32), 0, s, (const int*)counts, n_experts, kTM, offsets, tiles);
+  if ((rc = check_launch("moe_offsets"))) return rc;
+  launch_chained(moe_fill_kernel, dim3(n_experts), dim3(256), 0, s, (const int*)choice, n_pairs, (const int*)offsets, order);
+  return check_launch("moe_fill");
+}
+
+// gated != 0: act[list row][n_out] = silu(gate) * up from x (gathered, scaled); else parts[choice][token][n_out] from act rows.
+ERB_EXPORT int erb_moe_product(const void* a, int lda, const void* weights, const int* offsets, const int* tiles,
+                               const int* order, const float* score, int n_experts, int top, int n_tokens, int n_out, int k_dim,
+                               int gated, void* act, float* parts, void* stream) {
+  if (n_tokens <= 0) return ERB_OK;
+  if (n_out <= 0 || k_dim <= 0 || n_experts <= 0 || top <= 0) return fail(ERB_ERR_ARG, "moe_product: bad sizes");
+  const int max_tiles = (n_tokens * top + kTM - 1) / kTM + n_experts;
+  dim3 grid(max_tiles, (n_out + kTN - 1) / kTN);
+  if (gated)
+    launch_chained(moe_product_kernel<elem_t, true>, grid, dim3(256), 0, (cudaStream_t)stream, (const elem_t*)a, lda,
+                   (const elem_t*)weights, offsets, tiles, order, score, n_experts, top, n_tokens, n_out, k_dim, (elem_t*)act,
+                   parts);
+  else
+    launch_chained(moe_product_kernel<elem_t, false>, grid, dim3(256), 0, (cudaStream_t)stream, (const elem_t*)a, lda,
+                   (const elem_t*)weights, offsets, tiles, order, score, n_experts, top, n_tokens, n_out, k_dim, (elem_t*)act,
+                   parts);
+  return check_launch("moe_product");
+}

@@ -133,13 +133,15 @@ class StepContext:
         return self.granule_pages * self.page_size
 
     def decode_splits(self, window: int, split_keys: int = kernels.DECODE_SPLIT_KEYS) -> int:
-        """Largest number of key splits any single-token sequence of the batch has."""
+        """Largest number of key splits any single-token sequence of the batch has.  ``window`` as the attention
+        kernels take their mask: positive a window, negative the size of a chunk of a mask of chunks, 0 neither."""
+        reach = abs(window)
         if self.graph_key is not None:   # a captured layout: the bound must hold for every replay
             bound = -(-(self.bound_pages * self.page_size) // split_keys)
-            return bound if window <= 0 else min(bound, window // split_keys + 2)
+            return bound if reach == 0 else min(bound, reach // split_keys + 2)
         most = 1
         for pos in self.host_positions_last[: self.n_decode]:
-            lo = max(0, pos - window + 1) if window > 0 else 0
+            lo = max(0, pos - window + 1) if window > 0 else (pos - pos % reach if window < 0 else 0)
             most = max(most, pos // split_keys - lo // split_keys + 1)
         return most
 

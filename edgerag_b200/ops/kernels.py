@@ -94,6 +94,19 @@ _SIGNATURES = {
                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_gated_group_norm": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_float, c_void_p],
+    "erb_rms_between": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p,
+                        c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "erb_bias_rows": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "erb_qkv_whole_norm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                           c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p],
+    "erb_delta_scan": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "erb_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_void_p, c_void_p, c_void_p],
+    "erb_moe_product": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                        c_int, c_int, c_void_p, c_void_p, c_void_p],
     "erb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
@@ -101,7 +114,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
-_LAUNCHES = {"erb_linear_batched": 0, "erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
+_LAUNCHES = {"erb_moe_route": 4, "erb_linear_batched": 0, "erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
 SKINNY_MAX_ROWS = 16     # rows up to which the register-fed weight-streaming kernels are used
 TC_MAX_ROWS = 64         # rows up to which the TMA + tcgen05 weight-streaming kernel may be used
 
@@ -274,6 +287,89 @@ def add_layernorm(hidden: torch.Tensor, weight: torch.Tensor | None, bias: torch
     _call(_fn("elementwise", _ELEM[elem], "erb_add_layernorm"), hidden.data_ptr(), _ptr(delta), delta.shape[0] if in_parts else 0,
           delta.stride(0) if in_parts else 0, _ptr(pw), _ptr(pb), float(peps), _ptr(weight), _ptr(bias), float(eps), _ptr(out),
           int(out_ld), _ptr(rows), n, h, int(write_back and rows is None), _stream())
+
+
+def rms_between(hidden: torch.Tensor, out: torch.Tensor | None, *, weight: torch.Tensor | None = None, eps: float = 0.0,
+                delta: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+                post: tuple[torch.Tensor, float] | None = None, own: tuple[torch.Tensor, float] | None = None,
+                rows: torch.Tensor | None = None, write_back: bool = True, dtype: torch.dtype | None = None) -> None:
+    """The residual add between RMS norms, everything in float with eps inside the root.  In order: with ``own = (w,
+    eps)`` the stream's rows are normed in place; the update ``delta`` (rows of the element type, or float32 partial
+    sums ``[parts, rows, width]`` added in order and rounded to the element type once) gets ``bias`` added and, with
+    ``post = (w, eps)``, is normed (kept float); ``hidden +=`` the update, in place when ``write_back``; ``out`` (None:
+    nothing) receives the row rounded once: normed with ``weight`` and ``eps``, or as it is where ``weight`` is None.
+    ``rows`` picks the rows that ``out`` gets (then nothing is written back).  ``dtype`` names the element type where
+    neither ``out`` nor ``delta`` does."""
+    _need(hidden, "hidden", torch.float32); _need(weight, "weight", torch.float32); _need(bias, "bias", torch.float32)
+    _need(out, "out", contiguous=False); _need(rows, "rows", torch.int32)
+    h = hidden.shape[1]
+    in_parts = delta is not None and delta.dim() == 3
+    elem = out.dtype if out is not None else (delta.dtype if delta is not None and not in_parts else dtype)
+    if elem is None:
+        raise KernelError("rms_between: nothing names the element type")
+    _need(delta, "delta", torch.float32 if in_parts else elem)
+    if delta is not None and delta.shape[-2:] != hidden.shape:
+        raise KernelError("rms_between: delta and hidden disagree")
+    if (bias is not None or post is not None) and delta is None:
+        raise KernelError("rms_between: a bias or a closing norm needs an update")
+    for pair in (post, own):
+        if pair is not None:
+            _need(pair[0], "norm weight", torch.float32)
+            if pair[0].numel() != h:
+                raise KernelError("rms_between: a norm's weight must have the row's width")
+    if (weight is not None and weight.numel() != h) or (bias is not None and bias.numel() != h):
+        raise KernelError("rms_between: vectors must have the row's width")
+    if out is not None:
+        n = out.shape[0]
+        if out.shape[1] != h or out.stride(1) != 1:
+            raise KernelError("rms_between: out must be [rows, width] with unit inner stride")
+        if rows is None and n != hidden.shape[0]:
+            raise KernelError("rms_between: out rows differ from hidden rows")
+        if rows is not None and rows.numel() < n:
+            raise KernelError("rms_between: fewer row indices than output rows")
+        out_ld = out.stride(0) if n > 1 else max(h, out.stride(0))
+    else:
+        n, out_ld = hidden.shape[0], h
+        if rows is not None:
+            raise KernelError("rms_between: a selection of rows needs an output")
+    _call(_fn("elementwise", _ELEM[elem], "erb_rms_between"), hidden.data_ptr(), _ptr(delta), delta.shape[0] if in_parts else 0,
+          delta.stride(0) if in_parts else 0, _ptr(bias), _ptr(own[0]) if own else None, float(own[1]) if own else 0.0,
+          _ptr(post[0]) if post else None, float(post[1]) if post else 0.0, _ptr(weight), float(eps), _ptr(out), int(out_ld),
+          _ptr(rows), n, h, int(write_back and rows is None), _stream())
+
+
+def qkv_whole_norm(qkv: torch.Tensor, positions: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, *,
+                   q_count: int, k_count: int, eps: float, q_bias: torch.Tensor | None = None, k_bias: torch.Tensor | None = None,
+                   v_bias: torch.Tensor | None = None, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
+                   inv_freq: torch.Tensor | None = None, rot_dim: int = 0, has_kv: bool = True, slots: torch.Tensor | None = None,
+                   k_pages: torch.Tensor | None = None, v_pages: torch.Tensor | None = None, page_size: int = 16) -> None:
+    """Rows ``[q heads | k heads | v heads]`` (``head_dim`` entries a head; with ``has_kv`` False the queries only) made
+    ready for attention where the norm of queries and keys runs over a token's whole projection: biases added, ``q *
+    rsqrt(sum(q^2) / q_count + eps) * q_norm`` (all entries of the row at once; ``q_count`` is the true number of
+    entries where heads are padded with zeros), k likewise, entries ``i`` and ``i + rot_dim / 2`` of the first
+    ``rot_dim`` of every q and k head turned by ``position * inv_freq[i]``; q goes back in place, k and v (plus bias)
+    to the tokens' cache slots.  All in float."""
+    _need(qkv, "qkv", contiguous=False); _need(positions, "positions", torch.int32)
+    for name, t in (("q_bias", q_bias), ("k_bias", k_bias), ("v_bias", v_bias), ("q_norm", q_norm), ("k_norm", k_norm),
+                    ("inv_freq", inv_freq)):
+        _need(t, name, torch.float32)
+    _need(slots, "slots", torch.int32); _need(k_pages, "k_pages", qkv.dtype); _need(v_pages, "v_pages", qkv.dtype)
+    n = qkv.shape[0]
+    qw, kw = n_q_heads * head_dim, n_kv_heads * head_dim
+    if qkv.stride(1) != 1 or qkv.shape[1] < qw + (2 * kw if has_kv else 0):
+        raise KernelError("qkv_whole_norm: rows too narrow")
+    for t, width in ((q_bias, qw), (q_norm, qw), (k_bias, kw), (k_norm, kw), (v_bias, kw)):
+        if t is not None and t.numel() != width:
+            raise KernelError("qkv_whole_norm: a bias or norm weight has the wrong size")
+    if rot_dim and (inv_freq is None or inv_freq.numel() < rot_dim // 2):
+        raise KernelError("qkv_whole_norm: too few frequencies")
+    if k_pages is not None and (tuple(k_pages.shape[1:]) != (n_kv_heads, page_size, head_dim) or v_pages is None
+                                or v_pages.shape != k_pages.shape or slots is None or slots.numel() < n):
+        raise KernelError("qkv_whole_norm: pages or slots disagree with the heads")
+    _call(_fn("elementwise", _elem(qkv), "erb_qkv_whole_norm"), qkv.data_ptr(), qkv.stride(0) if n > 1 else qkv.shape[1],
+          _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), _ptr(q_norm), _ptr(k_norm), int(q_count), int(k_count), float(eps),
+          positions.data_ptr(), _ptr(inv_freq), int(rot_dim), _ptr(slots), _ptr(k_pages), _ptr(v_pages), n, n_q_heads,
+          n_kv_heads, head_dim, int(page_size), int(bool(has_kv)), _stream())
 
 
 def cast_rows(src: torch.Tensor, dst: torch.Tensor) -> None:
@@ -925,15 +1021,138 @@ def gated_group_norm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, e
           float(eps), _stream())
 
 
+# --- the gated delta rule ------------------------------------------------------------------------
+
+DELTA_MAX_KEY_DIM = 512      # entries of a key the scan kernel holds per column (32 lanes of 16)
+
+
+def delta_scan(qkv: torch.Tensor, proj: torch.Tensor, off_b: int, off_a: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+               state: torch.Tensor, n_seqs: int, seq_starts: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor,
+               n_key_heads: int, key_dim: int) -> None:
+    """The gated delta rule over every request's rows, from and to its record in ``state`` (float ``[slots, heads,
+    vdim, key_dim]``, the matrix of a head stored with the value index first).  ``qkv``: convolved and activated rows
+    ``[q (key heads * key_dim) | k (the same) | v (heads * vdim)]``; the raw write strengths and decay inputs are
+    columns ``off_b .. off_b + heads`` and ``off_a .. off_a + heads`` of ``proj``.  Per token and head: q and k are
+    made unit vectors (q also times ``key_dim ** -0.5``), ``beta = sigmoid(b)``, ``g = exp(-exp(a_log) * softplus(a +
+    dt_bias))``, ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``.  ``out`` float ``[tokens, heads * vdim]``."""
+    _need(qkv, "qkv"); _need(proj, "proj", qkv.dtype, contiguous=False); _need(state, "state", torch.float32)
+    _need(out, "out", torch.float32); _need(dt_bias, "dt_bias", torch.float32); _need(a_log, "a_log", torch.float32)
+    _need(seq_starts, "seq_starts", torch.int32); _need(state_slots, "state_slots", torch.int32)
+    n = qkv.shape[0]
+    _, heads, vdim, d = state.shape
+    if d != key_dim or qkv.shape[1] != 2 * n_key_heads * d + heads * vdim or out.shape != (n, heads * vdim) or \
+            proj.shape[0] != n or max(off_b, off_a) + heads > proj.shape[1] or dt_bias.numel() != heads or \
+            a_log.numel() != heads or heads % n_key_heads or seq_starts.numel() < n_seqs + 1 or state_slots.numel() < n_seqs:
+        raise KernelError("delta_scan: shapes disagree")
+    _call(_fn("delta", _elem(qkv), "erb_delta_scan"), qkv.data_ptr(), qkv.shape[1], proj.data_ptr(),
+          proj.stride(0) if n > 1 else proj.shape[1], int(off_b), int(off_a), dt_bias.data_ptr(), a_log.data_ptr(),
+          state.data_ptr(), seq_starts.data_ptr(), state_slots.data_ptr(), out.data_ptr(), int(n_seqs), n, heads,
+          int(n_key_heads), d, vdim, _stream())
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_heads: int, eps: float) -> None:
+    """out = o / sqrt(mean(o^2) + eps) * weight * silu(gate), the mean taken over every head's ``vdim`` entries, one
+    weight vector of ``vdim`` entries for all heads.  ``o`` float ``[tokens, heads * vdim]``; ``gate`` a view with unit
+    inner stride and ``out`` of the element type."""
+    _need(o, "o", torch.float32); _need(gate, "gate", out.dtype, contiguous=False); _need(weight, "weight", torch.float32)
+    _need(out, "out")
+    n, width = o.shape
+    if width % n_heads or weight.numel() != width // n_heads or out.shape != (n, width) or gate.shape != (n, width) or \
+            gate.stride(1) != 1:
+        raise KernelError("head_norm_gate: shapes disagree")
+    _call(_fn("delta", _elem(out), "erb_head_norm_gate"), o.data_ptr(), gate.data_ptr(), gate.stride(0) if n > 1 else width,
+          weight.data_ptr(), out.data_ptr(), n, int(n_heads), width // n_heads, float(eps), _stream())
+
+
+# --- routed experts ------------------------------------------------------------------------------
+
+def moe_tile_rows() -> int:
+    """Rows of one tile of the experts' products: an expert's list of rows is walked in tiles of this many."""
+    return int(_fn("moe", "float32", "erb_moe_tile_rows")())
+
+
+def moe_lists_ints(n_tokens: int, n_experts: int, top: int) -> int:
+    """int32 entries of the scratch ``moe_route`` fills: choices and order per pair, counts, offsets, tile offsets."""
+    return 2 * n_tokens * top + 3 * (n_experts + 1)
+
+
+def _moe_lists(lists: torch.Tensor, n_tokens: int, n_experts: int, top: int):
+    pairs = n_tokens * top
+    if lists.numel() < moe_lists_ints(n_tokens, n_experts, top):
+        raise KernelError("moe: the scratch of lists is too small")
+    e1 = n_experts + 1
+    choice, order = lists[:pairs], lists[pairs: 2 * pairs]
+    counts, offsets, tiles = (lists[2 * pairs + i * e1: 2 * pairs + (i + 1) * e1] for i in range(3))
+    return choice, order, counts, offsets, tiles
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, lists: torch.Tensor, score: torch.Tensor) -> None:
+    """Route every row of ``x`` (element type, row-strided view allowed): logits ``w_router x`` in float (``w_router``
+    float ``[experts, width]``), the ``top`` largest chosen (the lower index wins a tie), ``score`` float ``[tokens *
+    top]`` their sigmoids; ``lists`` (int32, ``moe_lists_ints`` entries) receives the choices and, per expert, the list
+    of its (token, choice) pairs in rising order with offsets, all made on the device."""
+    _need(x, "x", contiguous=False); _need(w_router, "w_router", torch.float32); _need(lists, "lists", torch.int32)
+    _need(score, "score", torch.float32)
+    n, width = x.shape
+    n_experts = w_router.shape[0]
+    if w_router.shape[1] != width or x.stride(1) != 1 or score.numel() < n * top:
+        raise KernelError("moe_route: shapes disagree")
+    choice, order, counts, offsets, tiles = _moe_lists(lists, n, n_experts, top)
+    _call(_fn("moe", _elem(x), "erb_moe_route"), x.data_ptr(), x.stride(0) if n > 1 else width, w_router.data_ptr(), n, width,
+          n_experts, int(top), choice.data_ptr(), score.data_ptr(), counts.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
+          order.data_ptr(), _stream())
+
+
+def moe_gate_up(x: torch.Tensor, w_gate_up: torch.Tensor, lists: torch.Tensor, score: torch.Tensor, top: int,
+                act: torch.Tensor) -> None:
+    """act[list row] = silu(W_gate r) * (W_up r) with ``r = round(score * x[token])`` for every (token, choice) pair,
+    in the order of the experts' lists.  ``w_gate_up`` ``[experts, 2 * ff, width]`` (gate rows, then up rows)."""
+    _need(x, "x", contiguous=False); _need(w_gate_up, "w_gate_up", x.dtype); _need(act, "act", x.dtype)
+    n, width = x.shape
+    n_experts, two_ff, k = w_gate_up.shape
+    if k != width or two_ff % 2 or act.shape != (n * top, two_ff // 2) or x.stride(1) != 1:
+        raise KernelError("moe_gate_up: shapes disagree")
+    _, order, _, offsets, tiles = _moe_lists(lists, n, n_experts, top)
+    _call(_fn("moe", _elem(x), "erb_moe_product"), x.data_ptr(), x.stride(0) if n > 1 else width, w_gate_up.data_ptr(),
+          offsets.data_ptr(), tiles.data_ptr(), order.data_ptr(), score.data_ptr(), n_experts, int(top), n, two_ff // 2, width,
+          1, act.data_ptr(), None, _stream())
+
+
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, lists: torch.Tensor, top: int, parts: torch.Tensor) -> None:
+    """parts[choice, token] = W_down[expert] act[list row]: float ``[>= top, tokens, width]`` partial sums of the
+    tokens' updates, one per choice.  ``w_down`` ``[experts, width, ff]``."""
+    _need(act, "act"); _need(w_down, "w_down", act.dtype); _need(parts, "parts", torch.float32)
+    n_experts, width, ff = w_down.shape
+    n = act.shape[0] // top
+    if act.shape != (n * top, ff) or parts.dim() != 3 or parts.shape[0] < top or parts.shape[1:] != (n, width):
+        raise KernelError("moe_down: shapes disagree")
+    _, order, _, offsets, tiles = _moe_lists(lists, n, n_experts, top)
+    _call(_fn("moe", _elem(act), "erb_moe_product"), act.data_ptr(), ff, w_down.data_ptr(), offsets.data_ptr(),
+          tiles.data_ptr(), order.data_ptr(), None, n_experts, int(top), n, width, ff, 0, None, parts.data_ptr(), _stream())
+
+
 # --- attention -------------------------------------------------------------------------------
 
 DECODE_SPLIT_KEYS = 512
 
+
+def mask_reach(window: int, chunk: int) -> int:
+    """The one integer in which the attention kernels take their mask: a window as it is, a mask of chunks as
+    the negative of the chunk's size, 0 for plain causal attention."""
+    if window and chunk:
+        raise KernelError("attention: a window and a mask of chunks exclude each other")
+    if window < 0 or chunk < 0:
+        raise KernelError("attention: window and chunk must not be negative")
+    return int(window) if window else -int(chunk)
+
+
 def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                    seq_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
-                   scale: float, window: int = 0, keep_first: int = 0) -> None:
+                   scale: float, window: int = 0, keep_first: int = 0, chunk: int = 0) -> None:
     """Causal attention of every token over its sequence's pages (general kernel, any portion sizes).
     ``window`` > 0: a query sees the last ``window`` keys (its own included) and the first ``keep_first`` of the sequence.
+    ``chunk`` > 0 (instead of a window): a query sees the earlier keys of its own run of ``chunk`` positions, runs
+    counted from position 0 of the sequence.
 
     ``q``: ``[tokens, >= n_q_heads * D]`` view with unit inner stride (the q part of a qkv buffer);
     ``out``: ``[tokens, n_q_heads * D]``; pages ``[n_pages, n_kv_heads, page_size, D]``;
@@ -948,7 +1167,7 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
         raise KernelError("attention_rows: q/out layout disagrees with the head counts")
     _call(_fn("attention", _elem(q), "erb_attention_rows"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], seq_of_token.data_ptr(),
-          positions.data_ptr(), out.data_ptr(), out.stride(0), n, n_q_heads, nkv, d, page_size, int(window),
+          positions.data_ptr(), out.data_ptr(), out.stride(0), n, n_q_heads, nkv, d, page_size, mask_reach(window, chunk),
           int(keep_first), float(scale), _stream())
 
 
@@ -1067,9 +1286,10 @@ def decode_scratch_floats(n_seqs: int, n_q_heads: int, head_dim: int, max_splits
 def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                      token_of_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
                      scale: float, part_acc: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
-                     window: int = 0, split_keys: int = DECODE_SPLIT_KEYS, keep_first: int = 0) -> None:
+                     window: int = 0, split_keys: int = DECODE_SPLIT_KEYS, keep_first: int = 0, chunk: int = 0) -> None:
     """Attention of one new token per sequence, keys cut into splits of ``split_keys`` (split-KV).
     With a window the first ``keep_first`` keys stay visible; the first split of the window takes them along.
+    ``chunk`` > 0 (instead of a window): the mask of chunks of ``attention_rows``.
 
     ``token_of_seq`` int32 ``[sequences]`` gives each sequence's row in q/out/positions.  Scratch:
     ``part_acc`` float ``[sequences * heads * max_splits * D]``, ``part_ml`` twice
@@ -1089,8 +1309,8 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     _call(_fn("attention", _elem(q), "erb_attention_decode"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(),
-          max_splits, n_seqs, n_q_heads, nkv, d, page_size, int(window), int(keep_first), int(split_keys), float(scale),
-          _stream())
+          max_splits, n_seqs, n_q_heads, nkv, d, page_size, mask_reach(window, chunk), int(keep_first), int(split_keys),
+          float(scale), _stream())
 
 
 def decode_bulk_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_heads: int, n_kv_heads: int,

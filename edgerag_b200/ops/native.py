@@ -33,6 +33,8 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...], bool]] = {
     "attention": ("attention.cu", (), True),
     "latent_attention": ("latent_attention.cu", (), True),
     "ssm": ("ssm.cu", (), True),
+    "delta": ("delta.cu", (), True),
+    "moe": ("moe.cu", (), True),
     "attention_tc": ("attention_tc.cu", ("-lcuda",), False),
     "attention_prefill": ("attention_prefill.cu", ("-lcuda",), False),
     "gemm": ("gemm.cu", ("-lcublasLt",), True),

@@ -15,6 +15,14 @@ encoding (``values_are_keys``: no value projection; the cache still holds keys a
 names (``names``).  With any of bias, norm or shared values the step after the product is one kernel
 (``kernels.qk_prepare``) that also writes the cache.
 
+A second family of options, also one kernel after the product (``kernels.qkv_whole_norm``): biases on all four
+projections (``all_bias``; the output's rides with the update to whoever adds it), a unit-RMS norm over a token's whole
+query projection and whole key projection with a weight per entry (``whole_norm_eps``), values of another size than
+queries and keys (``v_dim``), and a mask of chunks (``chunk``: a query sees the earlier keys of its own run of ``chunk``
+positions, runs counted from the sequence's start; no key is ever out of every later query's sight, so the cache
+keeps all pages).  Heads whose sizes differ or are no multiple of 8 are stored padded with zeros to one size ``D``:
+scores and outputs are unchanged, and the norm's mean divides by the true count.
+
 Single new tokens go through the split-KV decode kernels, portions of prompts through the tensor-core
 kernel (bfloat16, heads of 64, with or without a window) or the row kernel; all read keys and values straight from the pages (no gather copy, unlike
 edgerag/cache/paged.py:208-238).
@@ -36,9 +44,25 @@ class Attention(Mixer):
     def __init__(self, hidden: int, n_q_heads: int, n_kv_heads: int, head_dim: int, position: PartSpec,
                  dtype: torch.dtype, device: torch.device, window: int = 0, own_kv: bool = True,
                  scale: float | None = None, keep_first: int = 0, qk_bias: bool = False, qk_norm_eps: float | None = None,
-                 values_are_keys: bool = False, names: dict[str, str] | None = None) -> None:
+                 values_are_keys: bool = False, names: dict[str, str] | None = None, chunk: int = 0, v_dim: int | None = None,
+                 all_bias: bool = False, whole_norm_eps: float | None = None) -> None:
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} query heads are not divisible by {n_kv_heads} kv heads")
+        self.chunk = int(chunk or 0)
+        self.all_bias, self.whole_norm_eps = bool(all_bias), whole_norm_eps
+        self.has_update_bias = self.all_bias
+        #: true sizes of a query/key head and of a value head; ``head_dim`` below is the size they are stored in
+        self.qk_dim = head_dim
+        self.v_dim = head_dim if v_dim is None else int(v_dim)
+        widest = max(self.qk_dim, self.v_dim)
+        padded = -(-widest // 8) * 8 if widest <= 128 else -(-widest // 16) * 16
+        #: the second family's kernel handles padded heads, a norm over the projection and the four biases
+        self.whole = self.all_bias or whole_norm_eps is not None or padded != self.qk_dim or self.v_dim != self.qk_dim
+        if self.whole and (qk_bias or qk_norm_eps is not None or values_are_keys):
+            raise ValueError("attention: the two families of options exclude each other")
+        if self.chunk < 0 or (self.chunk and window):
+            raise ValueError("attention: a mask of chunks takes a positive size and excludes a window")
+        head_dim = padded if self.whole else head_dim
         self.hidden, self.n_q, self.n_kv, self.head_dim = hidden, n_q_heads, n_kv_heads, head_dim
         self.window = int(window or 0)
         self.keep_first = int(keep_first or 0) if self.window > 0 else 0
@@ -46,9 +70,9 @@ class Attention(Mixer):
         if (self.qk_bias or self.qk_norm_eps is not None or self.values_are_keys) and not own_kv:
             raise ValueError("biases, head norms and shared values need the layer's own keys")
         self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-                      "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight",
-                      **(names or {})}
-        self.q_bias = self.k_bias = self.q_norm = self.k_norm = None
+                      "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias",
+                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", **(names or {})}
+        self.q_bias = self.k_bias = self.v_bias = self.q_norm = self.k_norm = None
         self.own_kv = own_kv
         self.scale = float(head_dim ** -0.5 if scale is None else scale)
         self.dtype, self.device = dtype, device
@@ -56,6 +80,8 @@ class Attention(Mixer):
         self.q_width = n_q_heads * head_dim
         self.kv_width = n_kv_heads * head_dim
         self.in_width = self.q_width + (1 if self.values_are_keys else 2) * self.kv_width
+        if self.whole and not own_kv:
+            self.in_width = self.q_width         # queries only: keys and values are another layer's
         self.w_qkv: torch.Tensor | None = None
         self.w_o: torch.Tensor | None = None
 
@@ -64,6 +90,8 @@ class Attention(Mixer):
 
     def weight_specs(self) -> list[WeightSpec]:
         nm = self.names
+        if self.whole:
+            return self._whole_specs()
         specs = [WeightSpec(nm["q"], (self.q_width, self.hidden))]
         if self.own_kv:
             specs.append(WeightSpec(nm["k"], (self.kv_width, self.hidden)))
@@ -75,8 +103,59 @@ class Attention(Mixer):
             specs += [WeightSpec(nm["q_norm"], (self.head_dim,), "vector32"), WeightSpec(nm["k_norm"], (self.head_dim,), "vector32")]
         return specs + [WeightSpec(nm["o"], (self.hidden, self.q_width))]
 
+    def _whole_specs(self) -> list[WeightSpec]:
+        """The tensors of the second family of options, in their true (unpadded) sizes."""
+        nm = self.names
+        q_true, k_true, v_true = self.n_q * self.qk_dim, self.n_kv * self.qk_dim, self.n_kv * self.v_dim
+        specs = [WeightSpec(nm["q"], (q_true, self.hidden))]
+        if self.all_bias:
+            specs.append(WeightSpec(nm["q_bias"], (q_true,), "vector32"))
+        if self.whole_norm_eps is not None:
+            specs.append(WeightSpec(nm["q_norm"], (q_true,), "vector32"))
+        if self.own_kv:
+            specs += [WeightSpec(nm["k"], (k_true, self.hidden)), WeightSpec(nm["v"], (v_true, self.hidden))]
+            if self.all_bias:
+                specs += [WeightSpec(nm["k_bias"], (k_true,), "vector32"), WeightSpec(nm["v_bias"], (v_true,), "vector32")]
+            if self.whole_norm_eps is not None:
+                specs.append(WeightSpec(nm["k_norm"], (k_true,), "vector32"))
+        specs.append(WeightSpec(nm["o"], (self.hidden, self.n_q * self.v_dim)))
+        if self.all_bias:
+            specs.append(WeightSpec(nm["o_bias"], (self.hidden,), "vector32"))
+        return specs
+
+    def _pad_heads(self, t: torch.Tensor, heads: int, true: int, dtype: torch.dtype) -> torch.Tensor:
+        """Rows (or entries) ``[heads * true, ...]`` re-laid as ``[heads * head_dim, ...]``, zeros in the padding."""
+        t = t.to(device=self.device, dtype=dtype)
+        if true == self.head_dim:
+            return t.contiguous()
+        out = torch.zeros((heads, self.head_dim) + tuple(t.shape[1:]), dtype=dtype, device=self.device)
+        out[:, :true] = t.reshape((heads, true) + tuple(t.shape[1:]))
+        return out.reshape((heads * self.head_dim,) + tuple(t.shape[1:])).contiguous()
+
+    def _load_whole(self, tensors: dict[str, torch.Tensor]) -> None:
+        nm, f32 = self.names, torch.float32
+        parts = [self._pad_heads(tensors[nm["q"]], self.n_q, self.qk_dim, self.dtype)]
+        if self.own_kv:
+            parts += [self._pad_heads(tensors[nm["k"]], self.n_kv, self.qk_dim, self.dtype),
+                      self._pad_heads(tensors[nm["v"]], self.n_kv, self.v_dim, self.dtype)]
+        self.w_qkv = torch.cat(parts, dim=0).contiguous()
+        w_o = tensors[nm["o"]].to(device=self.device, dtype=self.dtype)            # [hidden, heads * v_dim]: pad the columns
+        self.w_o = self._pad_heads(w_o.t(), self.n_q, self.v_dim, self.dtype).t().contiguous()
+        if self.all_bias:
+            self.q_bias = self._pad_heads(tensors[nm["q_bias"]], self.n_q, self.qk_dim, f32)
+            self.update_bias = tensors[nm["o_bias"]].to(device=self.device, dtype=f32).contiguous()
+            if self.own_kv:
+                self.k_bias = self._pad_heads(tensors[nm["k_bias"]], self.n_kv, self.qk_dim, f32)
+                self.v_bias = self._pad_heads(tensors[nm["v_bias"]], self.n_kv, self.v_dim, f32)
+        if self.whole_norm_eps is not None:
+            self.q_norm = self._pad_heads(tensors[nm["q_norm"]], self.n_q, self.qk_dim, f32)
+            if self.own_kv:
+                self.k_norm = self._pad_heads(tensors[nm["k_norm"]], self.n_kv, self.qk_dim, f32)
+
     def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
         nm = self.names
+        if self.whole:
+            return self._load_whole(tensors)
         f32 = lambda t: t.to(device=self.device, dtype=torch.float32).contiguous()   # noqa: E731
         if self.own_kv:
             parts = [tensors[nm["q"]], tensors[nm["k"]]] + ([] if self.values_are_keys else [tensors[nm["v"]]])
@@ -93,6 +172,18 @@ class Attention(Mixer):
     def _prepare(self, x, qkv, ctx, pages, slots) -> None:
         """The input product and everything between it and the attention: biases, head norms, positions, cache write."""
         d = self.head_dim
+        if self.whole:
+            pos = self.position
+            if getattr(pos, "pairs", False):
+                raise ValueError("attention: with these options positions turn the halves of a head's first entries")
+            kernels.linear(x, self.w_qkv, qkv)
+            kernels.qkv_whole_norm(qkv, ctx.positions, self.n_q, self.n_kv, d, q_count=self.n_q * self.qk_dim,
+                                   k_count=self.n_kv * self.qk_dim, eps=self.whole_norm_eps or 0.0, q_bias=self.q_bias,
+                                   k_bias=self.k_bias, v_bias=self.v_bias, q_norm=self.q_norm, k_norm=self.k_norm,
+                                   inv_freq=getattr(pos, "inv_freq", None), rot_dim=getattr(pos, "rot_dim", 0),
+                                   has_kv=self.own_kv, slots=slots, k_pages=None if pages is None else pages[0],
+                                   v_pages=None if pages is None else pages[1], page_size=ctx.page_size)
+            return
         if self.qk_bias or self.qk_norm_eps is not None or self.values_are_keys:
             pos = self.position
             kernels.linear(x, self.w_qkv, qkv)
@@ -119,6 +210,8 @@ class Attention(Mixer):
         out = ctx.buf("attn.out", (n, self.q_width), self.dtype)
         tables = ctx.block_tables[group]
         nd = ctx.n_decode
+        if self.chunk:
+            return self._project_out(self._chunked(qkv, out, k_pages, v_pages, tables, ctx), ctx)
         if nd:
             # Under a window a token reads few keys, and the grouped-heads kernel takes all kv heads it can into one block:
             # with few (sequence, kv head) pairs the bulk-copy kernel's finer plan wins (8 sequences of 4 kv heads: a decode
@@ -170,6 +263,26 @@ class Attention(Mixer):
         elif n > nd:
             kernels.attention_rows(qkv[nd:], k_pages, v_pages, tables, ctx.seq_of_token[nd:], ctx.positions[nd:],
                                    out[nd:], self.n_q, self.scale, window=self.window, keep_first=self.keep_first)
+        return self._project_out(out, ctx)
+
+    def _chunked(self, qkv, out, k_pages, v_pages, tables, ctx) -> torch.Tensor:
+        """Attention under a mask of chunks: single new tokens through the split-KV kernel, portions through the row kernel."""
+        nd, n, d = ctx.n_decode, qkv.shape[0], self.head_dim
+        if nd:
+            split = kernels.DECODE_SPLIT_KEYS
+            max_splits = ctx.decode_splits(-self.chunk, split)
+            need_acc, need_ml = kernels.decode_scratch_floats(nd, self.n_q, d, max_splits)
+            part_acc = ctx.buf("attn.part_acc", (need_acc,), torch.float32)
+            part_ml = ctx.buf("attn.part_ml", (need_ml,), torch.float32)
+            kernels.attention_decode(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions, out[:nd],
+                                     self.n_q, self.scale, part_acc, part_ml, max_splits, split_keys=split, chunk=self.chunk)
+        if n > nd:
+            kernels.attention_rows(qkv[nd:], k_pages, v_pages, tables, ctx.seq_of_token[nd:], ctx.positions[nd:], out[nd:],
+                                   self.n_q, self.scale, chunk=self.chunk)
+        return out
+
+    def _project_out(self, out: torch.Tensor, ctx) -> torch.Tensor:
+        n = out.shape[0]
         n_parts = kernels.linear_parts_count(out, self.w_o)
         if n_parts:      # the rows of a larger decode step: k split over the SMs, the norm after adds the parts
             y = ctx.buf("mixer.out_parts", (n_parts, n, self.hidden), torch.float32)

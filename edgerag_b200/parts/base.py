@@ -102,6 +102,8 @@ class NormedUpdate:
 
     tensor: torch.Tensor
     norm: "Norm"
+    #: a float vector added to every row of ``tensor`` before the norm acts (a projection's bias that rides along)
+    bias: "torch.Tensor | None" = None
 
 
 @dataclass
@@ -175,6 +177,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    #: a float vector that belongs on every row of the update ``forward`` returns (the bias of an output projection);
+    #: the block adds it as it adds the update.  The property is read after ``load_weights``.
+    update_bias: "torch.Tensor | None" = None
+    has_update_bias = False
+
     def cache_spec(self) -> KVGroupSpec | list[StateSpec] | None:
         """What one call of this mixer keeps between steps: paged keys/values (``n_layers`` is
         ignored), state records of fixed size, or nothing."""
@@ -218,7 +225,10 @@ def settle_update(hidden: torch.Tensor, delta: "torch.Tensor | NormedUpdate | No
     if delta is None:
         return
     if isinstance(delta, NormedUpdate):
-        delta.norm.add_normed(hidden, delta.tensor)
+        if delta.bias is not None:
+            delta.norm.add_normed(hidden, delta.tensor, bias=delta.bias)
+        else:
+            delta.norm.add_normed(hidden, delta.tensor)
     else:
         kernels.residual_add(hidden, delta, dtype)
 

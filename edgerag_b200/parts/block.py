@@ -6,7 +6,8 @@ follows it, so a block receives the previous block's update as ``delta`` and ret
 feed-forward output as the update that is still to be added.
 
 ``SandwichBlock`` has a norm on both sides of each sublayer: ``h += post1(mixer(norm1(h))); h += post2(ffn(norm2(h)))``.
-The closing norms belong to the block (their tensors sit beside the layer's other norms).  An update leaves a
+The closing norms belong to the block (their tensors sit beside the layer's other norms).  With the ``pass`` norm in
+the opening places it is the arrangement whose sublayers read the stream itself and norm only what they add.  An update leaves a
 sublayer as a ``NormedUpdate``, so that the closing norm, the residual add and the norm that opens the next
 sublayer run as one kernel where the norms have one.
 """
@@ -26,6 +27,8 @@ class PreNormBlock(Block):
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm | None, ffn: FeedForward | None, hidden: int,
                  dtype: torch.dtype, device: torch.device) -> None:
         """``norm2`` and ``ffn`` are None for a layer that is its mixer's sublayer only."""
+        if getattr(mixer, "has_update_bias", False):
+            raise ValueError("a mixer whose update carries a bias needs a block that closes the update with a norm")
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
         self.hidden = hidden
         self.dtype = dtype
@@ -82,7 +85,7 @@ class SandwichBlock(Block):
         self.norm1.forward(hidden, x, delta)             # hidden += (closed) delta; x = norm1(hidden)
         if delta is not None:
             ctx.stream_written = kernels.launches()
-        mixed = NormedUpdate(self.mixer.forward(x, ctx, call), self.post1)
+        mixed = NormedUpdate(self.mixer.forward(x, ctx, call), self.post1, self.mixer.update_bias)
         if self.ffn is None:
             return mixed                                  # closed and added by whichever norm comes next
         self.norm2.forward(hidden, x, mixed)             # hidden += post1(mixed); x = norm2(hidden)

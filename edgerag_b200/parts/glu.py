@@ -46,6 +46,12 @@ class BoundedGLU(FeedForward):
         self.w_down = cast(tensors[down]).contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        y = ctx.buf("ffn.out", (x.shape[0], self.hidden), self.dtype)
+        self.forward_into(x, ctx, y)
+        return y
+
+    def forward_into(self, x: torch.Tensor, ctx, y: torch.Tensor) -> None:
+        """The update written to ``y``: rows of the element type or float32 (one of a sum of parts that a caller keeps)."""
         n = x.shape[0]
         act = ctx.buf("ffn.act", (n, self.intermediate), self.dtype)
         if kernels.linear_glu_supported(x, self.w_gate_up):
@@ -55,6 +61,4 @@ class BoundedGLU(FeedForward):
             gate_up = ctx.buf("ffn.gate_up", (n, 2 * self.intermediate), self.dtype)
             kernels.linear(x, self.w_gate_up, gate_up)
             kernels.glu_bounded(gate_up, act, self.limit, self.alpha, self.shift, self.act)
-        y = ctx.buf("ffn.out", (n, self.hidden), self.dtype)
         kernels.linear(act, self.w_down, y)
-        return y

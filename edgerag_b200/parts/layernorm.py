@@ -46,6 +46,8 @@ class LayerNorm(Norm):
         return None, None
 
     def forward(self, hidden, out, delta=None, rows=None, write_back=True, settled=False) -> None:
+        if isinstance(delta, NormedUpdate) and delta.bias is not None:
+            raise ValueError("a layer norm has no kernel for an update that carries a bias")
         if isinstance(delta, NormedUpdate) and not isinstance(delta.norm, LayerNorm):
             if rows is not None or not write_back:
                 raise ValueError("a pending update closed by another kind of norm can only be added to all rows")

@@ -40,10 +40,56 @@ class RMSNorm(Norm):
         self.weight = (w + self.weight_offset if self.weight_offset else w).contiguous()
 
     def forward(self, hidden, out, delta=None, rows=None, write_back=True, settled=False) -> None:
-        if isinstance(delta, NormedUpdate):        # closed by its own norm and added first (no fused kernel for that here)
+        if isinstance(delta, NormedUpdate):
+            post = delta.norm
+            if isinstance(post, RMSNorm) and not post.weight_offset and not self.weight_offset:
+                # the closing norm, the add and this norm in one kernel, all float
+                kernels.rms_between(hidden, out, weight=self.weight, eps=self.eps, delta=delta.tensor, bias=delta.bias,
+                                    post=(post.weight, post.eps), rows=rows, write_back=write_back)
+                return
             if rows is not None or not write_back:
-                raise ValueError("a pending update that a norm has to close can only be added to all rows")
+                raise ValueError("a pending update that another kind of norm has to close can only be added to all rows")
             settle_update(hidden, delta, self.dtype)
             delta, settled = None, False
         kernels.add_rmsnorm(hidden, self.weight, out, self.eps, delta=delta, rows=rows, write_back=write_back, settled=settled,
                             exact=self.exact)
+
+    def add_normed(self, hidden: torch.Tensor, x: torch.Tensor, bias: torch.Tensor | None = None) -> None:
+        kernels.rms_between(hidden, None, delta=x, bias=bias, post=(self._plain_weight(), self.eps), dtype=self.dtype)
+
+    def add_normed_cast(self, hidden: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor,
+                        bias: torch.Tensor | None = None, write_back: bool = False) -> None:
+        """``out = cast(hidden + self(x + bias))`` (``x`` None: the plain cast); ``hidden`` keeps the sum when ``write_back``."""
+        kernels.rms_between(hidden, out, delta=x, bias=bias, post=None if x is None else (self._plain_weight(), self.eps),
+                            write_back=write_back)
+
+    def norm_stream(self, hidden: torch.Tensor) -> None:
+        """``hidden = self(hidden)`` in place, in float (a norm that acts on the stream itself, as after an embedding)."""
+        kernels.rms_between(hidden, None, own=(self._plain_weight(), self.eps), dtype=self.dtype)
+
+    def _plain_weight(self) -> torch.Tensor:
+        return self.weight        # (the offset was added when the tensor was loaded)
+
+
+@register_part("norm", "pass")
+class PassNorm(Norm):
+    """No norm: a sublayer that reads the residual stream as it is.  ``out`` receives the stream (plus the pending
+    update) rounded to the element type; a pending update that a norm has to close is closed in the same kernel
+    where that norm has one (``add_normed_cast``)."""
+
+    graph_safe = True
+
+    def __init__(self, dtype: torch.dtype, device: torch.device, size: int | None = None, **_unused) -> None:
+        self.dtype, self.device, self.size = dtype, device, size
+
+    def forward(self, hidden, out, delta=None, rows=None, write_back=True, settled=False) -> None:
+        post = bias = None
+        if isinstance(delta, NormedUpdate):
+            if isinstance(delta.norm, RMSNorm):
+                post, bias, delta = (delta.norm.weight, delta.norm.eps), delta.bias, delta.tensor
+            else:
+                if rows is not None or not write_back:
+                    raise ValueError("a pending update that another kind of norm has to close can only be added to all rows")
+                settle_update(hidden, delta, self.dtype)
+                delta = None
+        kernels.rms_between(hidden, out, delta=delta, bias=bias, post=post, rows=rows, write_back=write_back)

@@ -28,13 +28,18 @@ class RotaryHalves(PositionEncoding):
     pairs = False            # which entries make a pair: (i, i + rot_dim / 2)
 
     def __init__(self, head_dim: int, theta: float, dtype: torch.dtype, device: torch.device,
-                 rot_dim: int | None = None) -> None:
+                 rot_dim: int | None = None, precise: bool = False) -> None:
+        """``precise``: the frequencies ``theta ** (-2j / rot_dim)`` are made in float64 and rounded to float32 once
+        (otherwise in float32 arithmetic, as the Llama decoder's reference does)."""
         self.head_dim = head_dim
         self.rot_dim = head_dim if rot_dim is None else rot_dim
         if self.rot_dim % 2 or not 0 < self.rot_dim <= head_dim:
             raise ValueError(f"rot_dim {self.rot_dim} must be even and at most head_dim {head_dim}")
         self.theta = float(theta)
-        inv_freq = 1.0 / (self.theta ** (torch.arange(0, self.rot_dim, 2, dtype=torch.int64).float() / self.rot_dim))
+        if precise:
+            inv_freq = self.theta ** (-torch.arange(0, self.rot_dim, 2, dtype=torch.float64) / self.rot_dim)
+        else:
+            inv_freq = 1.0 / (self.theta ** (torch.arange(0, self.rot_dim, 2, dtype=torch.int64).float() / self.rot_dim))
         self.inv_freq = inv_freq.to(device=device, dtype=torch.float32).contiguous()
 
     def apply_and_store(self, qkv, ctx, n_q_heads, n_kv_heads, head_dim, pages, slots) -> None:
