@@ -556,6 +556,31 @@ def vokusun_config(size: dict, n_runs: int) -> dict:
             "loop": {"start": 1, "stop": 3, "times": 2} if looped else None}
 
 
+#: the Lozanex sizes beside DESIGN_SIZES: heads of 64 under a mask of chunks, delta-rule heads of 128 x 128, and routed
+#: experts whose chosen ones plus the shared expert are as wide as the dense feed-forward of the size (top * ff / 8 + ff / 2)
+LOZANEX_CHUNK = 1024
+LOZANEX_EXPERTS = {"experts": 32, "top": 4}
+
+
+def lozanex_config(size: dict, n_layers: int) -> dict:
+    """Layers in the order delta rule, attention under a mask of chunks, delta rule, attention on the cache of the
+    attention layer two before; every layer with routed experts and a shared expert; repeated."""
+    heads = size["width"] // 64
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 64, "scale": 64 ** -0.5,
+           "rot": {"base": 1000000.0, "dims": 32}, "mask": {"size": LOZANEX_CHUNK}}
+    delta = {"heads": size["width"] // 128, "kv_heads": max(1, size["width"] // 256), "dim": 128, "vdim": 128, "conv": 4}
+    mlp = {"kind": "moe", "expert": {"ff": size["ff"] // 8}, "router": dict(LOZANEX_EXPERTS), "shared": {"ff": size["ff"] // 2}}
+    layers = []
+    for i in range(n_layers):
+        if i % 2 == 0:
+            layers.append({"type": "delta", "mixer": dict(delta), "mlp": mlp})
+        elif i % 4 == 3:
+            layers.append({"type": "attention", "mixer": dict(att, kv_from=i - 2), "mlp": mlp})
+        else:
+            layers.append({"type": "attention", "mixer": dict(att), "mlp": mlp})
+    return {"architecture": "Lozanex", "width": size["width"], "vocab": size["vocab"], "norm": {"eps": 1e-5}, "layers": layers}
+
+
 def run_designs(args) -> dict:
     """Prefill (one portion of 2,048 tokens) and decode (batch 1 and --batch at a context of 2,048) of one design
     (--design) and of the Llama decoder at the same width, feed-forward size, vocabulary and number of layer
@@ -631,6 +656,8 @@ def run_designs(args) -> dict:
 
     if args.design == "vokusun":
         return run_vokusun(args, measure, n_layers, block, clocks, peak_source, microbench)
+    if args.design == "lozanex":
+        return run_lozanex(args, measure, n_layers, block, clocks, peak_source, microbench)
     for name, size in DESIGN_SIZES.items():
         out[name] = {"layers": n_layers, "dokodra": measure(dokodra_config(size, n_layers), size["vocab"]),
                      "llama": measure(llama_config(size, n_layers), size["vocab"])}
@@ -712,6 +739,66 @@ def run_vokusun(args, measure, n_runs: int, block: int, clocks, peak_source: str
             "sizes": out, "kernels": kern, "step_kernels": steps, "clocks": clocks.record()}
 
 
+def run_lozanex(args, measure, n_layers: int, block: int, clocks, peak_source: str, microbench) -> dict:
+    """Lozanex beside Dokodra (the framework's other design of recurrent and attention layers) at equal width, layer
+    count and feed-forward width per token, then its kernels beside the like kernels of that design and of the Llama
+    decoder at equal work, then which kernels a step of each spends its time in."""
+    import subprocess
+    import tempfile
+    import types
+
+    out: dict = {}
+    for name, size in DESIGN_SIZES.items():
+        out[name] = {"layers": n_layers, "lozanex": measure(lozanex_config(size, n_layers), size["vocab"]),
+                     "dokodra": measure(dokodra_config(size, n_layers), size["vocab"])}
+    size = DESIGN_SIZES["w2048"]
+    ssm = size["ssm"]
+    ns = lambda **kw: types.SimpleNamespace(dtype="bfloat16", iters=10, warmup=3, page=block, sequential_pages=False, **kw)  # noqa: E731
+    heads = dict(heads=32, kv_heads=8, head_dim=64)
+    pre = lambda tokens, **kw: microbench.prefill_attention(ns(tokens=tokens, past=0, kernel="tc", key_splits=0, **heads, **kw))  # noqa: E731
+    dec = lambda **kw: microbench.decode_attention(ns(batch=64, split=0, head_group=0, cold=True, **heads, **kw))  # noqa: E731
+    delta = dict(heads=16, head_dim=128, key_heads=8, key_dim=128)
+    scan = dict(heads=ssm["heads"], head_dim=ssm["vdim"], state=ssm["state"], groups=ssm["groups"])
+    moe = dict(width=size["width"], ff=size["ff"] // 8, **LOZANEX_EXPERTS)
+    kern = {
+        "chunk_attention_prefill_2048": pre(2048, chunk=LOZANEX_CHUNK),
+        "chunk_attention_prefill_8192": pre(8192, chunk=LOZANEX_CHUNK),
+        "llama_attention_prefill_2048": pre(2048),
+        # the last position of a context of 8192 under chunks of 1024 reads a whole chunk: the bytes of a context of 1024
+        "chunk_attention_decode_b64_ctx8192_gqa": dec(context=8192, kernel="gqa", chunk=LOZANEX_CHUNK),
+        "chunk_attention_decode_b64_ctx8192_bulk": dec(context=8192, kernel="bulk", chunk=LOZANEX_CHUNK),
+        "llama_attention_decode_b64_ctx1024_gqa": dec(context=1024, kernel="gqa"),
+        "llama_attention_decode_b64_ctx1024_bulk": dec(context=1024, kernel="bulk"),
+        "delta_scan_decode_b64": microbench.delta_scan(ns(batch=64, tokens=1, **delta)),
+        "delta_scan_prefill_2048": microbench.delta_scan(ns(batch=1, tokens=2048, **delta)),
+        "delta_scan_prefill_8x2048": microbench.delta_scan(ns(batch=8, tokens=2048, **delta)),
+        "ssm_scan_decode_b64": microbench.ssm_scan(ns(batch=64, tokens=1, **scan)),
+        "ssm_scan_prefill_2048": microbench.ssm_scan(ns(batch=1, tokens=2048, **scan)),
+        "ssm_scan_prefill_8x2048": microbench.ssm_scan(ns(batch=8, tokens=2048, **scan)),
+        "routed_experts_8_rows": microbench.routed_experts(ns(tokens=8, **moe)),
+        "routed_experts_64_rows": microbench.routed_experts(ns(tokens=64, **moe)),
+        "routed_experts_2048_rows": microbench.routed_experts(ns(tokens=2048, **moe)),
+    }
+    steps = {}
+    for name, cfg in (("lozanex", lozanex_config(size, 4)), ("dokodra", dokodra_config(size, 4))):
+        with tempfile.NamedTemporaryFile("w", suffix=".json") as f:
+            json.dump(cfg, f)
+            f.flush()
+            done = subprocess.run([sys.executable, "-m", "edgerag_b200.ops.microbench", "step-kernels", "--config-json", f.name,
+                                   "--batch", str(args.batch), "--context", "2048", "--tokens", "2048", "--iters", "4", "--rows", "16"],
+                                  cwd=str(ROOT), env=dict(os.environ, EDGERAG_B200_NO_CHAIN="1"), capture_output=True, text=True)
+        if done.returncode != 0:
+            raise RuntimeError(f"step-kernels of {name} failed: {done.stderr[-400:]}")
+        steps[name] = json.loads(done.stdout.strip().splitlines()[-1])
+    return {"metric": "design_compare", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "dtype": "bf16",
+            "data": "synthetic", "impl": "ours", "higher_is_better": True,
+            "config": {"designs": ["Lozanex", "Dokodra"], "prefill_tokens": 2048, "decode_context": 2048,
+                       "decode_batches": sorted({1, args.batch}), "page_tokens": block, "chunk": LOZANEX_CHUNK,
+                       "routed_experts": LOZANEX_EXPERTS, "peaks": peak_source,
+                       "l2": "decode: weights and cache larger than L2 at w2048; kernels: caches and weights rotated (cold)"},
+            "sizes": out, "kernels": kern, "step_kernels": steps, "clocks": clocks.record()}
+
+
 def _tensors_of(model) -> list:
     import torch
 
@@ -739,7 +826,7 @@ def main() -> int:
                     help="decode: the headline measurement; mixed / continuous: the serving workloads of the "
                          "256M and 500M decoders through Engine.generate; designs: prefill and decode of one design "
                          "(--design) beside the Llama decoder at equal sizes, and its kernels against their rooflines")
-    ap.add_argument("--design", choices=["dokodra", "vokusun"], default="dokodra",
+    ap.add_argument("--design", choices=["dokodra", "vokusun", "lozanex"], default="dokodra",
                     help="with --workload designs: the design that is measured beside the Llama decoder")
     ap.add_argument("--ref-cpu-check", action="store_true",
                     help="with --impl reference: a dry run of the reference arm's loop at toy sizes on the CPU")

@@ -137,7 +137,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   // `keep_first` keys of its sequence.  The block then walks the tiles that hold kept keys and lie before
   // its first row's window, and after them the tiles from that window's first key on: walk step i is key
   // tile i for i < n_kept and key tile i + skip from there.  Without a window the walk is the tiles themselves.
-  const int lo_block = window > 0 ? max(pos0 - window + 1, 0) : 0;
+  // A negative `window` is a mask of chunks: a row sees the keys from the first position of its own run of -window
+  // positions on (runs counted from position 0 of the sequence); the walk then starts at the tile of the first
+  // row's run, and nothing is kept.
+  const int lo_block = first_visible_key(pos0, window);
   const int n_kept = window > 0 ? min((keep_first + BN - 1) / BN, lo_block / BN) : 0;
   const int skip = lo_block / BN - n_kept;
   auto tile_of = [&](int i) { return i < n_kept ? i : i + skip; };
@@ -190,12 +193,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     // behind may have been given back to the pool: their entries of the block table are not read.)
     auto page_of = [&](int j) {
       const int first_key = tile_of(j) * BN + lane * page_size;
-      const bool seen = window <= 0 || first_key + page_size > lo_block || first_key < keep_first;
+      const bool seen = window == 0 || first_key + page_size > lo_block || first_key < keep_first;
       return (j < n_kv && lane < pages_per_tile && first_key <= last_key && seen) ? bt[first_key / page_size] : -1;
     };
     auto bring = [&](int j, int page, const CUtensorMap* map, uint32_t dst, uint32_t full, bool zero_rest) {
       const int n_pages = __popc(__ballot_sync(0xffffffffu, page >= 0));
-      if (zero_rest && window > 0 && page < 0 && lane < pages_per_tile && tile_of(j) * BN + lane * page_size <= last_key) {
+      if (zero_rest && window != 0 && page < 0 && lane < pages_per_tile && tile_of(j) * BN + lane * page_size <= last_key) {
         // the rows of a page that is not brought: nobody sees them (their P is zero), but whatever an earlier
         // tile left there would spoil 0 * x of the second product if it were no number
         uint4* rows_of_page = reinterpret_cast<uint4*>(smem + (dst - base) + (uint32_t)lane * page_bytes);
@@ -307,7 +310,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       ok = __all_sync(0xffffffffu, ok) != 0;             // the same answer for every lane: TMEM loads are collective
     };
     float m_ref = -INFINITY, l_run = 0.f;                // l_run: this thread's half of the row's sum
-    const int win_lo = window > 0 ? my_pos - window + 1 : INT_MIN;      // first key of this row's window
+    const int win_lo = first_visible_key(my_pos, window);               // first key of this row's window or chunk
     auto hidden = [&](int key) { return key > my_pos || (key < win_lo && key >= keep_first); };
     for (int j = j0; j < n_end[t]; ++j) {
       wait(kBarSFull + t, (j - j0) & 1);
@@ -315,7 +318,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       fence_after_sync();
       const int tile_key0 = tile_of(j) * BN, key0 = tile_key0 + half * 64;
       // some row of the query tile has hidden keys here: keys after its own, or keys before its window that are not kept
-      const bool diagonal = tile_key0 + BN - 1 > pos0 + t * BM || (window > 0 && tile_key0 < pos0 + t * BM + BM - window);
+      const bool diagonal = tile_key0 + BN - 1 > pos0 + t * BM || (window != 0 && tile_key0 < first_visible_key(pos0 + t * BM + BM - 1, window));
       // The exponentials are taken against the reference maximum of the tiles before, without looking
       // for this tile's maximum first: P is a floating-point number, so a reference that is too low by
       // many powers of two costs no precision.  Only when a row's sum shows that the reference is far
@@ -500,7 +503,8 @@ ERB_EXPORT int erb_attention_prefill_tc_supported(int head_dim, int page_size) {
 }
 
 // Portions of prompts only (bfloat16, head_dim 64, pages of 8 to 128 tokens, a power of two).  window > 0:
-// a row sees its last `window` keys (its own included) and the first `keep_first` keys of its sequence.  q / out: row t is token t of the batch; seq_starts: int32 [n_seqs + 1] token offsets of the
+// a row sees its last `window` keys (its own included) and the first `keep_first` keys of its sequence; window < 0:
+// a row sees the keys of its own run of -window positions up to itself.  q / out: row t is token t of the batch; seq_starts: int32 [n_seqs + 1] token offsets of the
 // sequences to process (consecutive rows of block_tables); n_blocks: sum over them of
 // ceil(length / 256) (an upper bound is fine); n_pool_pages: pages of k_pages / v_pages (the tensor
 // maps cover the whole pool).  status: device int, set non-zero if a block gave up waiting.
@@ -544,7 +548,7 @@ ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const v
   launch_chained(attention_prefill_kernel, dim3(nq, n_blocks, key_splits), dim3(kThreads), kSmemBytes, (cudaStream_t)stream, mk, mv,
                  (const __nv_bfloat16*)q, q_row_stride, block_tables, max_pages, seq_starts, positions,
                  (__nv_bfloat16*)out, out_row_stride, n_seqs, nq, nkv, page_size, scale_log2, status, key_splits, part_o, part_ml,
-                 window > 0 ? window : 0, window > 0 && keep_first > 0 ? keep_first : 0);
+                 window, window > 0 && keep_first > 0 ? keep_first : 0);
   if ((rc = check_launch("attention_prefill_tc")) || key_splits == 1) return rc;
   launch_chained(attention_prefill_merge_kernel, dim3((n_rows * nq + 3) / 4), dim3(128), 0, (cudaStream_t)stream, part_o, part_ml,
                  (__nv_bfloat16*)out, out_row_stride, first_row, n_rows, nq, key_splits);

@@ -163,7 +163,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
   // pages are copied, so the first split starts at the page of k_lo and the keys before k_lo are passed over.
   // The first split also walks, before its own keys, the kept keys that lie before everything the splits read
   // (pages the window has left behind, other than those of kept keys, may have been given back: they are not touched).
-  const int k_lo = window > 0 ? max(pos - window + 1, 0) : 0;
+  const int k_lo = first_visible_key(pos, window);   // (a negative window: a mask of chunks of -window positions)
   const int first_split = k_lo / split_keys;
   const int k_first = hg == 1 ? k_lo : (k_lo / page_size) * page_size;
   const int begin = max((first_split + split) * split_keys, k_first);
@@ -409,7 +409,7 @@ attention_decode_bulk_combine_kernel(const float* __restrict__ part_acc, const f
   __shared__ float s_red[2];
   const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
   const int t = token_of_seq[seq];
-  const int k_lo = window > 0 ? max(positions[t] - window + 1, 0) : 0;
+  const int k_lo = first_visible_key(positions[t], window);
   const int n_splits = min(positions[t] / split_keys - k_lo / split_keys + 1, max_splits);   // never beyond what the split kernel wrote
   const size_t base = ((size_t)seq * nq + h) * max_splits;
   float m_i = -INFINITY, l_i = 0.f;
@@ -585,7 +585,7 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int pos = positions[t];
   // A window: as in the kernel above (whole pages are copied, so the first split starts at the page of the window's
   // first key, the keys before it are masked, and the first split walks the kept keys first).
-  const int k_lo = window > 0 ? max(pos - window + 1, 0) : 0;
+  const int k_lo = first_visible_key(pos, window);   // (a negative window: a mask of chunks of -window positions)
   const int first_split = k_lo / split_keys;
   const int k_first = (k_lo / page_size) * page_size;
   const int begin = max((first_split + split) * split_keys, k_first);
@@ -826,7 +826,6 @@ ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const v
                                         int head_dim, int page_size, int split_keys, float scale, int* status,
                                         int* counters, int window, int keep_first, void* stream) {
   if (n_seqs <= 0) return ERB_OK;
-  window = window > 0 ? window : 0;
   keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
   if (!erb_attention_decode_gqa_supported(nq, nkv, head_dim, page_size, split_keys))
     return fail(ERB_ERR_UNSUPPORTED, "attention_decode_gqa: %d/%d heads of %d, pages of %d, splits of %d", nq, nkv,
@@ -888,7 +887,8 @@ ERB_EXPORT int erb_attention_decode_bulk_head_group(int nkv, int head_dim, int p
 // Same contract as the general decode entry point (scratch provided by the caller, splits at
 // absolute multiples of split_keys, counted from the one that holds the window's first key), for bfloat16
 // with head_dim 32 / 64 / 128, at most 8 query heads per kv head, and page rows that are 16-byte multiples.
-// window > 0: the token sees its last `window` keys (its own included) and the first `keep_first` ones.
+// window > 0: the token sees its last `window` keys (its own included) and the first `keep_first` ones;
+// window < 0: the keys of its own run of -window positions (runs counted from position 0) up to itself.
 ERB_EXPORT int erb_attention_decode_bulk(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                                          const int* block_tables, int max_pages, const int* token_of_seq,
                                          const int* positions, void* out, int out_row_stride, float* part_acc,
@@ -897,7 +897,6 @@ ERB_EXPORT int erb_attention_decode_bulk(const void* q, int q_row_stride, const 
                                          int head_group, int window, int keep_first, void* stream) {
   if (n_seqs <= 0) return ERB_OK;
   if (nq <= 0 || nkv <= 0 || nq % nkv) return fail(ERB_ERR_ARG, "attention_decode_bulk: bad head counts");
-  window = window > 0 ? window : 0;
   keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
   if (max_splits <= 0 || split_keys <= 0 || !part_acc || !part_ml || !status || page_size <= 0)
     return fail(ERB_ERR_ARG, "attention_decode_bulk: bad arguments");

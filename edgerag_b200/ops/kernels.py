@@ -1348,8 +1348,9 @@ def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
                           token_of_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
                           scale: float, part_acc: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
                           status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS, head_group: int = 0, window: int = 0,
-                          keep_first: int = 0) -> None:
+                          keep_first: int = 0, chunk: int = 0) -> None:
     """``attention_decode`` for bfloat16 with keys and values streamed by bulk asynchronous copies.
+    ``chunk`` > 0 (instead of a window): the mask of chunks of ``attention_rows``.
     ``window`` > 0: the last ``window`` keys and the first ``keep_first``; the splits are counted from the one
     that holds the window's first key, and the first of them also walks the kept keys.
     The splits of a sequence are merged by the block that finishes last (``split_counters``), so
@@ -1371,7 +1372,7 @@ def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
           n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(),
-          split_counters(q.device, n_seqs * nkv).data_ptr(), int(head_group), int(window), int(keep_first), _stream())
+          split_counters(q.device, n_seqs * nkv).data_ptr(), int(head_group), mask_reach(window, chunk), int(keep_first), _stream())
 
 
 @functools.lru_cache(maxsize=4096)
@@ -1388,7 +1389,8 @@ def decode_gqa_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_hea
 def attention_decode_gqa(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                          token_of_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
                          scale: float, part_acc: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
-                         status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS, window: int = 0, keep_first: int = 0) -> None:
+                         status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS, window: int = 0, keep_first: int = 0,
+                         chunk: int = 0) -> None:
     """``attention_decode`` for several query heads per kv head on tensor cores (``window`` and ``keep_first`` as in
     ``attention_decode_bulk``): the query heads of a
     kv head are the rows of one matrix tile, pages arrive by TMA tensor copies."""
@@ -1408,7 +1410,7 @@ def attention_decode_gqa(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
           v_pages.data_ptr(), n_pages, block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
           n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(),
-          split_counters(q.device, n_seqs * nkv).data_ptr(), int(window), int(keep_first), _stream())
+          split_counters(q.device, n_seqs * nkv).data_ptr(), mask_reach(window, chunk), int(keep_first), _stream())
 
 
 #: query rows of one (sequence, head) that a block of the tensor-core prefill kernel takes
@@ -1449,9 +1451,10 @@ def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
                          seq_starts: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_blocks: int,
                          n_q_heads: int, scale: float, status: torch.Tensor, key_splits: int = 1, first_row: int = 0,
                          part_o: torch.Tensor | None = None, part_ml: torch.Tensor | None = None, window: int = 0,
-                         keep_first: int = 0) -> None:
+                         keep_first: int = 0, chunk: int = 0) -> None:
     """Causal attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 64).  ``window`` > 0: a
     query sees the last ``window`` keys (its own included) and the first ``keep_first`` of its sequence.
+    ``chunk`` > 0 (instead of a window): the mask of chunks of ``attention_rows``.
 
     ``qkv`` / ``out``: row t is token t of the batch (the q heads lead each qkv row);
     ``seq_starts`` int32 ``[n + 1]``: token offsets of the n sequences to process, whose block tables
@@ -1478,7 +1481,7 @@ def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
           v_pages.data_ptr(), n_pages, block_tables.data_ptr(), block_tables.shape[1], seq_starts.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), n_seqs, int(n_blocks), n_q_heads, nkv, d, page_size,
           float(scale), status.data_ptr(), int(key_splits), int(first_row), qkv.shape[0] - int(first_row), _ptr(part_o), _ptr(part_ml),
-          int(window), int(keep_first), _stream())
+          mask_reach(window, chunk), int(keep_first), _stream())
     if key_splits > 1:
         launch_counts["own"] += 1          # the merge of the ranges
 

@@ -86,8 +86,10 @@ def _paged(batch: int, context: int, nkv: int, d: int, page: int, dtype, shuffle
 
 def decode_attention(a) -> dict:
     dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
-    window, keep = getattr(a, "window", 0), getattr(a, "keep_first", 0)
+    window, keep, chunk = getattr(a, "window", 0), getattr(a, "keep_first", 0), getattr(a, "chunk", 0)
     seen = min(a.context, window + keep) if window > 0 else a.context       # keys a query reads
+    if chunk > 0:           # the query is the context's last position: it reads its chunk up to itself
+        seen = (a.context - 1) % chunk + 1
     nbytes = 2 * a.batch * seen * a.kv_heads * a.head_dim * (2 if dtype == torch.bfloat16 else 4)
     # --cold: rotate over so many caches that each launch finds its keys and values in DRAM, as a
     # step does whose weights have passed through L2 since the layer's cache was last read
@@ -105,32 +107,33 @@ def decode_attention(a) -> dict:
     tok = torch.arange(a.batch, dtype=torch.int32, device="cuda")
     if a.split <= 0:        # as the engine chooses it: from the batch and a power-of-two bound on the context
         bound, granule = kernels.context_bound(-(-a.context // a.page))
-        if window > 0:
-            bound = min(bound, -(-(window + keep) // a.page))
+        if window > 0 or chunk > 0:
+            bound = min(bound, -(-(window + keep + chunk) // a.page))
             granule = bound
         a.split, heads = kernels.choose_decode_plan(a.batch, a.kv_heads, bound * a.page, a.page, a.head_dim, a.kernel != "bulk",
                                                     granule * a.page)
         a.head_group = a.head_group or heads
     splits = (a.context - 1) // a.split + 1
-    if window > 0:
-        splits = min(splits, window // a.split + 2)
+    if window > 0 or chunk > 0:
+        splits = min(splits, (window + chunk) // a.split + 2)
     acc_n, ml_n = kernels.decode_scratch_floats(a.batch, a.heads, a.head_dim, splits)
     acc, ml = torch.empty(acc_n, device="cuda"), torch.empty(ml_n, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     scale = a.head_dim ** -0.5
     if a.kernel == "gqa":
         fn = lambda: kernels.attention_decode_gqa(q, *cache(), tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
-                                                  status, split_keys=a.split, window=window, keep_first=keep)
+                                                  status, split_keys=a.split, window=window, keep_first=keep, chunk=chunk)
     elif a.kernel == "bulk":
         fn = lambda: kernels.attention_decode_bulk(q, *cache(), tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
-                                                   status, split_keys=a.split, head_group=a.head_group, window=window, keep_first=keep)
+                                                   status, split_keys=a.split, head_group=a.head_group, window=window, keep_first=keep,
+                                                   chunk=chunk)
     else:
         fn = lambda: kernels.attention_decode(q, *cache(), tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
-                                              split_keys=a.split, window=window, keep_first=keep)
+                                              split_keys=a.split, window=window, keep_first=keep, chunk=chunk)
     us = _time(fn, max(a.iters, 2 * reps), a.warmup)
     return {"case": "decode-attention", "kernel": a.kernel, "split": a.split, "head_group": a.head_group, "us": round(us, 2),
             "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4),
-            "status": int(status), "from_dram": bool(a.cold) or nbytes > 126e6, "window": window, "keep_first": keep}
+            "status": int(status), "from_dram": bool(a.cold) or nbytes > 126e6, "window": window, "keep_first": keep, "chunk": chunk}
 
 
 def prefill_attention(a) -> dict:
@@ -145,28 +148,32 @@ def prefill_attention(a) -> dict:
     seq_of = torch.zeros(a.tokens, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     scale = a.head_dim ** -0.5
-    window, keep = getattr(a, "window", 0), getattr(a, "keep_first", 0)
+    window, keep, chunk = getattr(a, "window", 0), getattr(a, "keep_first", 0), getattr(a, "chunk", 0)
     if a.kernel == "tc":
         blocks = kernels.prefill_tc_blocks([a.tokens])
-        reach = min(total, window + keep + kernels.PREFILL_TC_ROWS) if window > 0 else total
+        reach = min(total, window + keep + chunk + kernels.PREFILL_TC_ROWS) if window > 0 or chunk > 0 else total
         ranges = a.key_splits or kernels.prefill_tc_key_splits(blocks, a.heads, reach, qkv.device)
         need_o, need_ml = kernels.prefill_tc_scratch_floats(a.tokens, a.heads, ranges)
         part_o, part_ml = torch.empty(need_o, device="cuda"), torch.empty(need_ml, device="cuda")
         fn = lambda: kernels.attention_prefill_tc(qkv, kp, vp, tables, starts, pos, out, blocks, a.heads, scale, status,  # noqa: E731
-                                                  key_splits=ranges, part_o=part_o, part_ml=part_ml, window=window, keep_first=keep)
+                                                  key_splits=ranges, part_o=part_o, part_ml=part_ml, window=window, keep_first=keep,
+                                                  chunk=chunk)
     else:
         fn = lambda: kernels.attention_rows(qkv, kp, vp, tables, seq_of, pos, out, a.heads, scale, window=window,  # noqa: E731
-                                            keep_first=keep)
+                                            keep_first=keep, chunk=chunk)
     us = _time(fn, a.iters, a.warmup)
     if window > 0:      # (query, key) pairs that are seen: the window's keys and the kept ones before it
         p = torch.arange(a.past, total, dtype=torch.float64)
         lo = (p - window + 1).clamp_min(0)
         pairs = float((p - lo + 1 + torch.minimum(lo, torch.tensor(float(keep)))).sum())
+    elif chunk > 0:     # every query sees the keys of its own chunk up to itself
+        p = torch.arange(a.past, total, dtype=torch.float64)
+        pairs = float((p % chunk + 1).sum())
     else:
         pairs = a.tokens * a.past + a.tokens * (a.tokens + 1) / 2
     flops = 4.0 * a.heads * a.head_dim * pairs
     return {"case": "prefill-attention", "kernel": a.kernel, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
-            "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4), "status": int(status), "window": window, "keep_first": keep}
+            "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4), "status": int(status), "window": window, "keep_first": keep, "chunk": chunk}
 
 
 def linear(a) -> dict:
@@ -401,6 +408,78 @@ def ssm_scan(a) -> dict:
             "tokens_per_s": round(n / us * 1e6, 1), "from_dram": nbytes > 126e6}
 
 
+def delta_scan(a) -> dict:
+    """The gated delta rule's kernel: ``batch`` requests of ``tokens`` tokens each.  One token per request is bound by
+    the state it reads and writes; a prompt portion by the walk along its tokens."""
+    dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
+    inner, ch = a.heads * a.head_dim, a.heads * a.head_dim + 2 * a.key_heads * a.key_dim
+    n = a.batch * a.tokens
+    qkv = (torch.randn((n, ch), device="cuda") * 0.3).to(dtype)
+    proj = torch.randn((n, 2 * a.heads), device="cuda").to(dtype)
+    vec = [torch.randn(a.heads, device="cuda") for _ in range(2)]
+    state = torch.zeros((a.batch, a.heads, a.head_dim, a.key_dim), device="cuda")
+    y = torch.empty((n, inner), device="cuda")
+    starts = (torch.arange(a.batch + 1, dtype=torch.int32) * a.tokens).cuda()
+    slots = torch.arange(a.batch, dtype=torch.int32).cuda()
+    fn = lambda: kernels.delta_scan(qkv, proj, 0, a.heads, vec[0], vec[1], state, a.batch, starts, slots, y, a.key_heads, a.key_dim)  # noqa: E731
+    us = _time(fn, a.iters, a.warmup)
+    item = 2 if dtype == torch.bfloat16 else 4
+    nbytes = 2 * state.numel() * 4 + n * (ch * item + inner * 4)
+    flops = 8.0 * n * a.heads * a.key_dim * a.head_dim          # two read-outs, the decay and the write, each over the matrix
+    return {"case": "delta-scan", "us": round(us, 2), "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1),
+            "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4), "gflops": round(flops / us / 1e3, 1),
+            "tokens_per_s": round(n / us * 1e6, 1), "from_dram": nbytes > 126e6}
+
+
+def routed_experts(a) -> dict:
+    """The routed experts' three kernels (router with lists, gate/up product, down product) over ``tokens`` rows, and
+    the dense gated feed-forward of equal work per token (``top * ff`` wide) through the library product beside them.
+    Few rows are bound by the weights of the chosen experts (every expert's, from about ``experts / top`` rows on),
+    many rows by the products' arithmetic."""
+    dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
+    n, E, top, ff, h = a.tokens, a.experts, a.top, a.ff, a.width
+    item = 2 if dtype == torch.bfloat16 else 4
+    reps = max(1, int(300e6 // (3 * E * ff * h * item)) + 1)       # rotate over copies of the weights: more than L2 in total
+    wgu = [(torch.randn((E, 2 * ff, h), device="cuda") * 0.02).to(dtype) for _ in range(reps)]
+    wd = [(torch.randn((E, h, ff), device="cuda") * 0.02).to(dtype) for _ in range(reps)]
+    router = torch.randn((E, h), device="cuda") * 0.05
+    x = torch.randn((n, h), device="cuda").to(dtype)
+    lists = torch.empty(kernels.moe_lists_ints(n, E, top), dtype=torch.int32, device="cuda")
+    score = torch.empty(n * top, device="cuda")
+    act = torch.empty((n * top, ff), dtype=dtype, device="cuda")
+    parts = torch.empty((top, n, h), device="cuda")
+    state = {"i": 0}
+
+    def rotate():
+        state["i"] = (state["i"] + 1) % reps
+        return state["i"]
+
+    kernels.moe_route(x, router, top, lists, score)
+    used = int((lists[2 * n * top: 2 * n * top + E] > 0).sum())     # experts that some row chose
+    us_route = _time(lambda: kernels.moe_route(x, router, top, lists, score), a.iters, a.warmup)
+    us_up = _time(lambda: kernels.moe_gate_up(x, wgu[rotate()], lists, score, top, act), max(a.iters, 2 * reps), a.warmup)
+    us_down = _time(lambda: kernels.moe_down(act, wd[rotate()], lists, top, parts), max(a.iters, 2 * reps), a.warmup)
+    # the dense feed-forward of the same arithmetic per token
+    dgu = [(torch.randn((2 * top * ff, h), device="cuda") * 0.02).to(dtype) for _ in range(max(1, reps // 4))]
+    dd = [(torch.randn((h, top * ff), device="cuda") * 0.02).to(dtype) for _ in range(max(1, reps // 4))]
+    gu = torch.empty((n, 2 * top * ff), dtype=dtype, device="cuda")
+    dact = torch.empty((n, top * ff), dtype=dtype, device="cuda")
+    dout = torch.empty((n, h), dtype=dtype, device="cuda")
+    us_dense_up = _time(lambda: kernels.linear(x, dgu[rotate() % len(dgu)], gu), a.iters, a.warmup)
+    us_dense_down = _time(lambda: kernels.linear(dact, dd[rotate() % len(dd)], dout), a.iters, a.warmup)
+    flops_up, flops_down = 4.0 * n * top * ff * h, 2.0 * n * top * ff * h
+    bytes_up, bytes_down = used * 2 * ff * h * item + n * h * item + n * top * ff * item, used * ff * h * item + n * top * (ff * item + h * 4)
+
+    def line(us, flops, nbytes):
+        return {"us": round(us, 2), "tflops": round(flops / us / 1e6, 2), "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4),
+                "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4)}
+
+    dense_bytes_up, dense_bytes_down = 2 * top * ff * h * item + n * h * item, top * ff * h * item + n * top * ff * item
+    return {"case": "routed-experts", "tokens": n, "experts": E, "top": top, "ff": ff, "width": h, "experts_used": used,
+            "route_us": round(us_route, 2), "gate_up": line(us_up, flops_up, bytes_up), "down": line(us_down, flops_down, bytes_down),
+            "dense_gate_up": line(us_dense_up, flops_up, dense_bytes_up), "dense_down": line(us_dense_down, flops_down, dense_bytes_down)}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="edgerag_b200.ops.microbench", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="case", required=True)
@@ -416,6 +495,7 @@ def main(argv=None) -> int:
     att.add_argument("--page", type=int, default=16)
     att.add_argument("--window", type=int, default=0, help="keys a query sees behind itself (0: all)")
     att.add_argument("--keep-first", type=int, default=0, help="with a window: first keys that stay visible")
+    att.add_argument("--chunk", type=int, default=0, help="instead of a window: a query sees its own run of this many positions")
     att.add_argument("--sequential-pages", action="store_true", help="pages in order instead of shuffled")
     d = sub.add_parser("decode-attention", parents=[common, att])
     d.add_argument("--batch", type=int, default=8)
@@ -472,13 +552,26 @@ def main(argv=None) -> int:
     ss.add_argument("--groups", type=int, default=8)
     ss.add_argument("--batch", type=int, default=8)
     ss.add_argument("--tokens", type=int, default=1)
+    ds = sub.add_parser("delta-scan", parents=[common])
+    ds.add_argument("--heads", type=int, default=32)
+    ds.add_argument("--head-dim", type=int, default=128, help="entries of a value")
+    ds.add_argument("--key-heads", type=int, default=16)
+    ds.add_argument("--key-dim", type=int, default=128)
+    ds.add_argument("--batch", type=int, default=8)
+    ds.add_argument("--tokens", type=int, default=1)
+    re = sub.add_parser("routed-experts", parents=[common])
+    re.add_argument("--tokens", type=int, default=8)
+    re.add_argument("--width", type=int, default=2048)
+    re.add_argument("--ff", type=int, default=1024)
+    re.add_argument("--experts", type=int, default=32)
+    re.add_argument("--top", type=int, default=4)
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)
         return 1
     fn = {"decode-attention": decode_attention, "prefill-attention": prefill_attention, "linear": linear,
           "step-kernels": step_kernels, "step-timeline": step_timeline, "latent-attention": latent_attention,
-          "ssm-scan": ssm_scan}[a.case]
+          "ssm-scan": ssm_scan, "delta-scan": delta_scan, "routed-experts": routed_experts}[a.case]
     load_peaks(a.peaks)
     result = fn(a)
     result["peaks"] = PEAKS_FROM

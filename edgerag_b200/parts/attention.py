@@ -210,47 +210,47 @@ class Attention(Mixer):
         out = ctx.buf("attn.out", (n, self.q_width), self.dtype)
         tables = ctx.block_tables[group]
         nd = ctx.n_decode
-        if self.chunk:
-            return self._project_out(self._chunked(qkv, out, k_pages, v_pages, tables, ctx), ctx)
+        reach_mask = self.window or self.chunk                  # keys a token can see under its mask (0: all before it)
+        mask = kernels.mask_reach(self.window, self.chunk)      # the mask as the kernels take it
         if nd:
             # Under a window a token reads few keys, and the grouped-heads kernel takes all kv heads it can into one block:
             # with few (sequence, kv head) pairs the bulk-copy kernel's finer plan wins (8 sequences of 4 kv heads: a decode
             # step of 0.362 ms against 0.384 ms; 64 sequences of 8: 48 us against 40 us for the kernel alone).
-            may_group = self.window <= 0 or nd * self.n_kv >= 64
+            may_group = reach_mask <= 0 or nd * self.n_kv >= 64
             grouped = may_group and self.n_q != self.n_kv and kernels.decode_gqa_supported(
                 self.dtype, d, self.window, self.n_q, self.n_kv, ctx.page_size, kernels.DECODE_SPLIT_KEYS)
             if ctx.batch_invariant:     # one plan for every batch: a sequence's sums are then added in one order
                 split, heads_per_block = kernels.DECODE_SPLIT_KEYS, 0
-            elif self.window > 0:       # a token reads its window and the kept keys, however long its context is
-                reach = min(ctx.max_keys_bound(), -(-(self.window + self.keep_first) // ctx.page_size) * ctx.page_size)
+            elif reach_mask > 0:        # a token reads its window (or chunk) and the kept keys, however long its context is
+                reach = min(ctx.max_keys_bound(), -(-(reach_mask + self.keep_first) // ctx.page_size) * ctx.page_size)
                 split, heads_per_block = kernels.choose_decode_plan(nd, self.n_kv, reach, ctx.page_size, d,
                                                                     grouped or self.dtype != torch.bfloat16, reach)
             else:
                 split, heads_per_block = kernels.choose_decode_plan(nd, self.n_kv, ctx.max_keys_bound(), ctx.page_size, d,
                                                                     grouped or self.dtype != torch.bfloat16, ctx.keys_granule())
-            max_splits = ctx.decode_splits(self.window, split)
+            max_splits = ctx.decode_splits(mask, split)
             need_acc, need_ml = kernels.decode_scratch_floats(nd, self.n_q, d, max_splits)
             part_acc = ctx.buf("attn.part_acc", (need_acc,), torch.float32)
             part_ml = ctx.buf("attn.part_ml", (need_ml,), torch.float32)
             if may_group and kernels.decode_gqa_supported(self.dtype, d, self.window, self.n_q, self.n_kv, ctx.page_size, split, max_splits):
                 kernels.attention_decode_gqa(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                              out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits, ctx.status,
-                                             split_keys=split, window=self.window, keep_first=self.keep_first)
+                                             split_keys=split, window=self.window, keep_first=self.keep_first, chunk=self.chunk)
             elif kernels.decode_bulk_supported(self.dtype, d, self.window, self.n_q, self.n_kv, max_splits):
                 kernels.attention_decode_bulk(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                               out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits, ctx.status,
                                               split_keys=split, head_group=heads_per_block, window=self.window,
-                                              keep_first=self.keep_first)
+                                              keep_first=self.keep_first, chunk=self.chunk)
             else:
                 kernels.attention_decode(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                          out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits,
-                                         window=self.window, split_keys=split, keep_first=self.keep_first)
+                                         window=self.window, split_keys=split, keep_first=self.keep_first, chunk=self.chunk)
         if n > nd and kernels.prefill_tc_supported(self.dtype, d, self.window, ctx.page_size):
             blocks = kernels.prefill_tc_blocks(ctx.host_q_len[nd:])
             # a portion that is short against its past: its few blocks' keys are cut into ranges
             reach = ctx.max_keys_bound()
-            if self.window > 0:         # what a block of rows can see: its rows' windows and the kept first keys
-                reach = min(reach, self.window + kernels.PREFILL_TC_ROWS + self.keep_first)
+            if reach_mask > 0:          # what a block of rows can see: its rows' windows (or chunks) and the kept first keys
+                reach = min(reach, reach_mask + kernels.PREFILL_TC_ROWS + self.keep_first)
             ranges = kernels.prefill_tc_key_splits(blocks, self.n_q, reach, qkv.device)
             part_o = part_ml = None
             if ranges > 1:
@@ -259,27 +259,11 @@ class Attention(Mixer):
                 part_ml = ctx.buf("attn.range_ml", (need_ml,), torch.float32)
             kernels.attention_prefill_tc(qkv, k_pages, v_pages, tables[nd:], ctx.seq_starts[nd:], ctx.positions, out, blocks,
                                          self.n_q, self.scale, ctx.status, key_splits=ranges, first_row=nd, part_o=part_o,
-                                         part_ml=part_ml, window=self.window, keep_first=self.keep_first)
+                                         part_ml=part_ml, window=self.window, keep_first=self.keep_first, chunk=self.chunk)
         elif n > nd:
             kernels.attention_rows(qkv[nd:], k_pages, v_pages, tables, ctx.seq_of_token[nd:], ctx.positions[nd:],
-                                   out[nd:], self.n_q, self.scale, window=self.window, keep_first=self.keep_first)
+                                   out[nd:], self.n_q, self.scale, window=self.window, keep_first=self.keep_first, chunk=self.chunk)
         return self._project_out(out, ctx)
-
-    def _chunked(self, qkv, out, k_pages, v_pages, tables, ctx) -> torch.Tensor:
-        """Attention under a mask of chunks: single new tokens through the split-KV kernel, portions through the row kernel."""
-        nd, n, d = ctx.n_decode, qkv.shape[0], self.head_dim
-        if nd:
-            split = kernels.DECODE_SPLIT_KEYS
-            max_splits = ctx.decode_splits(-self.chunk, split)
-            need_acc, need_ml = kernels.decode_scratch_floats(nd, self.n_q, d, max_splits)
-            part_acc = ctx.buf("attn.part_acc", (need_acc,), torch.float32)
-            part_ml = ctx.buf("attn.part_ml", (need_ml,), torch.float32)
-            kernels.attention_decode(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions, out[:nd],
-                                     self.n_q, self.scale, part_acc, part_ml, max_splits, split_keys=split, chunk=self.chunk)
-        if n > nd:
-            kernels.attention_rows(qkv[nd:], k_pages, v_pages, tables, ctx.seq_of_token[nd:], ctx.positions[nd:], out[nd:],
-                                   self.n_q, self.scale, chunk=self.chunk)
-        return out
 
     def _project_out(self, out: torch.Tensor, ctx) -> torch.Tensor:
         n = out.shape[0]

@@ -155,8 +155,12 @@ def routed_choice(h: torch.Tensor, t: dict, pre: str, top: int):
     return idx, w
 
 
-def moe(h: torch.Tensor, mlp: dict, t: dict, pre: str) -> torch.Tensor:
+def moe(h: torch.Tensor, mlp: dict, t: dict, pre: str, chosen: torch.Tensor | None = None) -> torch.Tensor:
+    """``chosen`` [tokens, top]: experts to use instead of the router's own choice (their scores stay the router's)."""
     idx, w = routed_choice(h, t, pre, int(mlp["router"]["top"]))
+    if chosen is not None:
+        idx = chosen.long()
+        w = torch.gather(torch.sigmoid(h @ t[pre + "router"].to(F64).T), 1, idx)
     out = torch.zeros(h.shape[0], t[pre + "e0.down"].shape[0], dtype=F64)
     for e in range(int(mlp["router"]["experts"])):
         for slot in range(idx.shape[1]):
@@ -168,8 +172,16 @@ def moe(h: torch.Tensor, mlp: dict, t: dict, pre: str) -> torch.Tensor:
     return out
 
 
-def forward(config: dict, tensors: dict, tokens, return_layers: bool = False):
-    """Logits [tokens, vocab] of one whole sequence (float64); with ``return_layers`` also the stream after every layer."""
+def router_margins(config: dict, tensors: dict, tokens) -> torch.Tensor:
+    """Per layer with a feed-forward and token: the gap between the last chosen and the first not chosen router logit."""
+    gaps: list[torch.Tensor] = []
+    forward(config, tensors, tokens, _gaps=gaps)
+    return torch.stack(gaps) if gaps else torch.zeros(0, len(tokens), dtype=F64)
+
+
+def forward(config: dict, tensors: dict, tokens, return_layers: bool = False, chosen: dict | None = None, _gaps=None):
+    """Logits [tokens, vocab] of one whole sequence (float64); with ``return_layers`` also the stream after every layer.
+    ``chosen``: layer -> [tokens, top] experts that the layer's feed-forward is to use whatever its router says."""
     eps = float(config["norm"]["eps"])
     ids = torch.as_tensor(tokens, dtype=torch.long)
     x = rms_norm(tensors["embed"].to(F64)[ids], tensors["embed.norm"], eps)
@@ -189,7 +201,109 @@ def forward(config: dict, tensors: dict, tokens, return_layers: bool = False):
             raise ValueError(layer["type"])
         x = x + rms_norm(y, tensors[f"l{i}.norm1"], eps)
         if layer.get("mlp") is not None:
-            x = x + rms_norm(moe(x, layer["mlp"], tensors, f"l{i}.mlp."), tensors[f"l{i}.norm2"], eps)
+            if _gaps is not None:
+                z = torch.sort(x @ tensors[f"l{i}.mlp.router"].to(F64).T, dim=-1, descending=True).values
+                top = int(layer["mlp"]["router"]["top"])
+                _gaps.append(z[:, top - 1] - z[:, top] if top < z.shape[1] else torch.full_like(z[:, 0], math.inf))
+            x = x + rms_norm(moe(x, layer["mlp"], tensors, f"l{i}.mlp.", None if chosen is None else chosen.get(i)),
+                             tensors[f"l{i}.norm2"], eps)
         after.append(x.clone())
     logits = rms_norm(x, tensors["final.norm"], eps) @ tensors["head"].to(F64).T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+# --- small configurations and random weights for tests ------------------------------------------------
+
+def attention_layer(heads=4, kv_heads=2, dim=32, vdim=None, rot_dims=16, base=10000.0, size=24, scale=0.25, kv_from=None,
+                    experts=4, top=2, ff=48, shared_ff=40) -> dict:
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim if vdim is None else vdim, "scale": scale}
+    if rot_dims is not None:
+        mixer["rot"] = {"base": base, "dims": rot_dims}
+    if size is not None:
+        mixer["mask"] = {"size": size}
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
+    return {"type": "attention", "mixer": mixer, "mlp": moe_mlp(experts, top, ff, shared_ff)}
+
+
+def delta_layer(heads=4, kv_heads=2, dim=16, vdim=24, conv=4, experts=4, top=2, ff=48, shared_ff=40) -> dict:
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv},
+            "mlp": moe_mlp(experts, top, ff, shared_ff)}
+
+
+def moe_mlp(experts, top, ff, shared_ff):
+    if experts is None:
+        return None
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    if shared_ff is not None:
+        mlp["shared"] = {"ff": shared_ff}
+    return mlp
+
+
+def make_config(layers: list[dict], width=64, vocab=160, eps=1e-5) -> dict:
+    import copy
+    return {"architecture": "Lozanex", "width": width, "vocab": vocab, "norm": {"eps": eps}, "layers": copy.deepcopy(layers)}
+
+
+def tensor_shapes(config: dict) -> dict[str, tuple[int, ...]]:
+    w, shapes = config["width"], {}
+    shapes["embed"] = (config["vocab"], w)
+    shapes["embed.norm"] = (w,)
+    for i, layer in enumerate(config["layers"]):
+        m, pre = layer["mixer"], f"l{i}.mix."
+        H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
+        shapes[f"l{i}.norm1"] = (w,)
+        if layer["type"] == "attention":
+            shapes.update({pre + "q": (H * d, w), pre + "q.b": (H * d,), pre + "q.norm": (H * d,),
+                           pre + "o": (w, H * dv), pre + "o.b": (w,)})
+            if m.get("kv_from") is None:
+                shapes.update({pre + "k": (G * d, w), pre + "k.b": (G * d,), pre + "k.norm": (G * d,),
+                               pre + "v": (G * dv, w), pre + "v.b": (G * dv,)})
+        else:
+            taps = m["conv"]
+            shapes.update({pre + "q": (G * d, w), pre + "q.conv": (G * d, taps), pre + "k": (G * d, w), pre + "k.conv": (G * d, taps),
+                           pre + "v": (H * dv, w), pre + "v.conv": (H * dv, taps), pre + "b": (H, w), pre + "a": (H, w),
+                           pre + "A_log": (H,), pre + "dt_bias": (H,), pre + "norm": (dv,), pre + "g": (H * dv, w),
+                           pre + "o": (w, H * dv)})
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            shapes[f"l{i}.norm2"] = (w,)
+            f = f"l{i}.mlp."
+            shapes[f + "router"] = (mlp["router"]["experts"], w)
+            for e in range(mlp["router"]["experts"]):
+                shapes.update({f"{f}e{e}.gate": (mlp["expert"]["ff"], w), f"{f}e{e}.up": (mlp["expert"]["ff"], w),
+                               f"{f}e{e}.down": (w, mlp["expert"]["ff"])})
+            if mlp.get("shared") is not None:
+                shapes.update({f + "shared.gate": (mlp["shared"]["ff"], w), f + "shared.up": (mlp["shared"]["ff"], w),
+                               f + "shared.down": (w, mlp["shared"]["ff"])})
+    shapes["final.norm"] = (w,)
+    shapes["head"] = (config["vocab"], w)
+    return shapes
+
+
+def random_tensors(config: dict, seed: int) -> dict[str, torch.Tensor]:
+    """Seeded weights, rounded to bfloat16 (so that both number formats of the engine see the same values)."""
+    gen = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        last = name.rsplit(".", 1)[-1]
+        if name.endswith(".conv"):
+            t = torch.randn(shape, generator=gen) * 0.6
+        elif last == "A_log":
+            t = torch.log(0.3 + 2.0 * torch.rand(shape, generator=gen))      # decays neither all near 1 nor all near 0
+        elif last == "dt_bias":
+            t = torch.randn(shape, generator=gen) - 1.0
+        elif last == "router":
+            t = torch.randn(shape, generator=gen) * 3.0 / math.sqrt(shape[1])
+        elif len(shape) == 2:
+            t = torch.randn(shape, generator=gen) / math.sqrt(shape[1])
+            if ".mix." in name and last in ("q", "k"):
+                t = t * 2.0                                   # sharper scores: a wrong key shows
+            if last == "embed":
+                t = t * math.sqrt(shape[1])
+        elif last == "b":
+            t = 0.2 * torch.randn(shape, generator=gen)
+        else:                                                 # norm weights
+            t = 1.0 + 0.2 * torch.randn(shape, generator=gen)
+        out[name] = t.to(torch.bfloat16)
+    return out

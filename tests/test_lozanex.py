@@ -1,0 +1,1068 @@
+"""Lozanex through the engine against the plain implementation of ``plain_lozanex``.
+
+Small configurations with random weights of their own: head counts, key and value sizes (equal, unequal, no multiple
+of 8), rotated widths, chunk sizes, convolution lengths, expert counts and choices that differ from layer to layer and
+from test to test (also the degenerate ones: one key/value head, as many as heads, one expert chosen, all chosen, no
+shared expert, a layer without a feed-forward, no mask, no rotation, a convolution of two taps).  Every mechanism alone;
+whole prompts against token-by-token decoding and portions down to two tokens; unequal requests in one batch with pages
+and slots that are freed, poisoned and used again; keys made dominant just inside and just outside a chunk, at page
+borders and far away; long decoding over several chunks; greedy generation through ``Engine.generate`` and the scheduler;
+the trace replay program.
+
+In bfloat16 a router's close call may fall the other way than in the plain float64 implementation, which changes a
+token's experts, not the arithmetic under test.  So the bfloat16 comparisons hand the plain implementation the experts
+that the engine chose (read from the device lists of the feed-forward); float32 comparisons use the plain router.
+"""
+
+from __future__ import annotations
+
+import copy
+import json
+import math
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lozanex as plain
+
+ROOT = Path(__file__).resolve().parent.parent
+
+DEL = plain.delta_layer(heads=4, kv_heads=2, dim=16, vdim=24, conv=4, experts=4, top=2, ff=48, shared_ff=40)
+DEL_B = plain.delta_layer(heads=3, kv_heads=3, dim=40, vdim=8, conv=2, experts=3, top=3, ff=24, shared_ff=None)
+DEL_C = plain.delta_layer(heads=6, kv_heads=1, dim=24, vdim=40, conv=3, experts=None)
+ATT = plain.attention_layer(heads=4, kv_heads=2, dim=32, vdim=32, rot_dims=12, base=700.0, size=21, scale=0.3, experts=5, top=1, ff=40,
+                            shared_ff=56)
+ATT_B = plain.attention_layer(heads=3, kv_heads=3, dim=20, vdim=12, rot_dims=20, base=50000.0, size=40, scale=0.2, experts=2, top=2,
+                              ff=32, shared_ff=16)
+ATT_C = plain.attention_layer(heads=6, kv_heads=1, dim=16, vdim=48, rot_dims=8, base=10000.0, size=17, scale=0.35, experts=None)
+ATT_SHARES = plain.attention_layer(heads=2, kv_heads=2, dim=32, vdim=32, rot_dims=12, base=700.0, size=9, scale=0.4, kv_from=1,
+                                   experts=4, top=3, ff=16, shared_ff=24)
+
+FULL = plain.make_config([DEL, ATT, DEL_B, ATT_SHARES, ATT_C, DEL_C, DEL], width=80, vocab=203, eps=1e-5)
+
+
+def without(layer, *keys):
+    out = copy.deepcopy(layer)
+    for key in keys:
+        del out["mixer"][key]
+    return out
+
+
+ALONE = {
+    "delta": plain.make_config([DEL]),
+    "delta_all_key_heads_two_taps_all_experts": plain.make_config([DEL_B], width=72),
+    "delta_one_key_head_no_ffn": plain.make_config([DEL_C], width=48),
+    "chunks": plain.make_config([ATT]),
+    "chunks_odd_head_sizes_full_rotation": plain.make_config([ATT_B], width=72),
+    "chunks_one_kv_head_wide_values_no_ffn": plain.make_config([ATT_C], width=48),
+    "no_mask_no_rotation": plain.make_config([without(ATT, "mask", "rot")]),
+    "shared_keys": plain.make_config([DEL_C, ATT, ATT_SHARES], width=56),
+}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    from edgerag_b200.weights.safetensors_io import write_safetensors
+
+    base = tmp_path_factory.mktemp("lozanex")
+    made = {}
+
+    def get(name: str, raw: dict, seed: int = 0, edit=None):
+        if name not in made:
+            folder = base / name
+            folder.mkdir()
+            tensors = plain.random_tensors(raw, seed)
+            if edit is not None:
+                edit(tensors)
+            (folder / "config.json").write_text(json.dumps(raw))
+            write_safetensors(folder / "model.safetensors", tensors)
+            made[name] = (folder, raw, tensors)
+        return made[name]
+
+    return get
+
+
+def make_engine(folder, dtype, **over):
+    from edgerag_b200.engine.engine import Engine, EngineOptions
+
+    opts = dict(dtype=dtype, block_size=16, num_blocks=64, max_batch_size=4, max_step_tokens=512, max_model_len=1 << 20,
+                cuda_graphs=False, poison_freed_pages=True)
+    opts.update(over)
+    eng = Engine.from_pretrained(folder, EngineOptions(**opts))
+    eng.log = ChoiceLog(eng.model)
+    return eng
+
+
+class ChoiceLog:
+    """Records, for every layer with routed experts, the experts the engine chose for the rows of every step."""
+
+    def __init__(self, model) -> None:
+        self.steps: list[dict[int, torch.Tensor]] = []
+        for i, block in enumerate(model.blocks):
+            if block.ffn is not None:
+                block.ffn.forward = self._wrap(i, block.ffn)
+
+    def _wrap(self, layer, ffn):
+        inner = ffn.forward
+
+        def forward(x, ctx):
+            from edgerag_b200.ops import kernels
+
+            out = inner(x, ctx)
+            n = x.shape[0]
+            lists = ctx.buf("moe.lists", (kernels.moe_lists_ints(n, ffn.n_experts, ffn.top),), torch.int32)
+            if self.steps:
+                self.steps[-1][layer] = lists[: n * ffn.top].reshape(n, ffn.top).cpu().clone()
+            return out
+
+        return forward
+
+    def new_step(self) -> None:
+        self.steps.append({})
+
+    def of_rows(self, picks: list[tuple[int, int, int]]) -> dict[int, torch.Tensor]:
+        """layer -> [tokens, top] for a sequence whose tokens were rows ``first .. first + n`` of step ``s``, in order."""
+        layers = self.steps[picks[0][0]].keys()
+        return {layer: torch.cat([self.steps[s][layer][first: first + n] for s, first, n in picks]) for layer in layers}
+
+
+def feed(runner, rid, tokens, cuts, log: ChoiceLog | None = None):
+    """Feed one request alone in portions; the logits of every token, and (with ``log``) the engine's choices of experts."""
+    from edgerag_b200.engine.step import StepEntry
+
+    rows, pos, picks = [], 0, []
+    for c in cuts:
+        c = min(c, len(tokens) - pos)
+        if c <= 0:
+            break
+        if log is not None:
+            log.new_step()
+            picks.append((len(log.steps) - 1, 0, c))
+        out = runner.step([StepEntry(rid, tokens=tokens[pos: pos + c], want=list(range(c)))])
+        rows.append(out.float().cpu().clone())
+        pos += c
+    assert pos == len(tokens), "the cuts do not cover the tokens"
+    return torch.cat(rows), (log.of_rows(picks) if log is not None else None)
+
+
+def row_errors(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
+    d = got.double() - want.double()
+    d = d - d.mean(-1, keepdim=True)
+    w = want.double() - want.double().mean(-1, keepdim=True)
+    return d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-9)
+
+
+#: (worst row, mean over rows).  float32: only the order of sums differs from the plain implementation.  bfloat16:
+#: activations are rounded to 8 bits between the products, and every sublayer's output is brought to unit RMS, which
+#: carries a small output's rounding into the stream at full size: single rows of a model of 7 narrow layers reach 11 %.
+#: The float32 runs are the sharp ones; the models made to show a fault move rows by 50 % and more.
+BANDS = {"float32": (3e-4, 6e-5), "bfloat16": (2e-1, 3.5e-2)}
+
+
+def assert_close(got, want, dtype, what=""):
+    assert torch.isfinite(got).all(), f"{what} {dtype}: non-finite logits"
+    e = row_errors(got, want)
+    worst, mean = BANDS[dtype]
+    assert e.max() <= worst and e.mean() <= mean, f"{what} {dtype}: worst {e.max():.2e} (row {int(e.argmax())}), mean {e.mean():.2e}"
+
+
+def tokens_for(raw, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, raw["vocab"], (n,), generator=g).tolist()
+
+
+def check_request(eng, raw, tensors, toks, cuts, dtype, what):
+    """One request alone, fed in ``cuts``, against the plain implementation (bfloat16: with the engine's experts)."""
+    eng.runner.admit(what)
+    got, chosen = feed(eng.runner, what, toks, cuts, eng.log if dtype == "bfloat16" else None)
+    eng.runner.release(what)
+    want = plain.forward(raw, tensors, toks, chosen=chosen)
+    assert_close(got, want, dtype, what)
+    eng.cache.check_invariants()
+
+
+# --- configuration, plan, cache bookkeeping (CPU) ---------------------------------------------------
+
+def test_plan_names_every_tensor_and_shares_a_cache_layer():
+    from edgerag_b200.config.registry import architecture_of
+    from edgerag_b200.models.decoder import DecoderModel
+
+    arch = architecture_of(FULL)
+    cfg = arch.read_config(FULL, "test")
+    model = DecoderModel(arch.make_plan(cfg), torch.float32, torch.device("cpu"))
+    assert {s.name: tuple(s.shape) for s in model.weight_specs()} == plain.tensor_shapes(FULL)
+    calls = [(c.layer, c.cache_layer, c.writes_cache) for c in model.schedule]
+    assert calls == [(0, 0, True), (1, 1, True), (2, 2, True), (3, 1, False), (4, 3, True), (5, 4, True), (6, 5, True)]
+    # heads of 32 as they are; keys of 16 beside values of 48 are stored in 48
+    groups = {(g.n_kv_heads, g.head_dim, g.window): g.n_layers for g in model.cache_layout.groups}
+    assert groups == {(2, 32, 0): 1, (1, 48, 0): 1}
+    states = {s.name: tuple(s.shape) for s in model.cache_layout.states}
+    assert states == {"conv@0": (3, 2 * 32 + 96), "delta@0": (4, 24, 16), "conv@2": (1, 2 * 120 + 24), "delta@2": (3, 8, 40),
+                      "conv@4": (2, 2 * 24 + 240), "delta@4": (6, 40, 24), "conv@5": (3, 2 * 32 + 96), "delta@5": (4, 24, 16)}
+    assert model.graph_safe
+
+
+def test_configuration_errors_name_the_key():
+    from edgerag_b200.config.model_config import ConfigError
+    from edgerag_b200.models.lozanex import LozanexConfig
+
+    def broken(change):
+        raw = copy.deepcopy(ALONE["shared_keys"])
+        change(raw)
+        return raw
+
+    cases = [
+        (lambda r: r["layers"][0].update(type="mamba"), "unknown layer type"),
+        (lambda r: r["layers"][1]["mixer"].pop("kv_heads"), "kv_heads"),
+        (lambda r: r["layers"][1]["mixer"].update(kv_heads=3), "kv_heads must divide"),
+        (lambda r: r["layers"][1]["mixer"]["rot"].update(dims=34), "rot.dims"),
+        (lambda r: r["layers"][1]["mixer"]["mask"].pop("size"), "size"),
+        (lambda r: r["layers"][1]["mixer"].pop("scale"), "scale"),
+        (lambda r: r["layers"][0]["mixer"].pop("conv"), "conv"),
+        (lambda r: r["layers"][2]["mixer"].update(kv_from=0), "kv_from"),
+        (lambda r: r["layers"][2]["mixer"].update(kv_from=2), "kv_from"),
+        (lambda r: r["layers"][2]["mixer"]["rot"].update(base=9.0), "another rotation"),
+        (lambda r: r["layers"][1]["mlp"].update(kind="dense"), "mlp.kind"),
+        (lambda r: r["layers"][1]["mlp"]["router"].update(top=9), "router.top"),
+        (lambda r: r.pop("norm"), "norm"),
+    ]
+    for change, word in cases:
+        with pytest.raises(ConfigError, match=word):
+            LozanexConfig.from_dict(broken(change), "t")
+
+
+def test_plain_mask_of_chunks_against_its_definition():
+    m = plain.chunk_mask(30, 41, 11, 7)                       # queries at positions 11 .. 40
+    for a in range(30):
+        for j in range(41):
+            i = 11 + a
+            assert bool(m[a, j]) == (j <= i and i // 7 == j // 7)
+    assert m[3, 14] and not m[3, 13] and m[2, 13] and not m[2, 14]          # position 14 opens a chunk, 13 closes one
+    assert plain.chunk_mask(9, 9, 0, 0).equal(torch.tril(torch.ones(9, 9, dtype=torch.bool)))
+
+
+def test_plain_rotation_turns_halves_and_keeps_the_rest():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(5, 2, 10, generator=g, dtype=torch.float64)
+    pos = torch.tensor([0, 3, 8, 21, 400])
+    y = plain.rotate_halves(x, pos, 100.0, 6)
+    assert torch.equal(y[..., 6:], x[..., 6:]) and torch.allclose(y[0], x[0])
+    assert torch.allclose(y[..., :6].pow(2).sum(-1), x[..., :6].pow(2).sum(-1))
+    a = 21 * 100.0 ** (-2.0 / 6)                                # entries 1 and 4 of the token at position 21
+    assert torch.allclose(y[3, 1, 1], x[3, 1, 1] * math.cos(a) - x[3, 1, 4] * math.sin(a))
+    assert torch.allclose(y[3, 1, 4], x[3, 1, 4] * math.cos(a) + x[3, 1, 1] * math.sin(a))
+
+
+def test_plain_delta_rule_by_hand():
+    """Two tokens of one head: the first write is beta v along k; the second decays it, corrects it and is read at once."""
+    k = torch.tensor([[[1.0, 0.0]], [[0.6, 0.8]]], dtype=torch.float64)
+    q = torch.tensor([[[0.5, 0.5]], [[1.0, 0.0]]], dtype=torch.float64)
+    v = torch.tensor([[[2.0, 4.0, 6.0]], [[1.0, 1.0, 1.0]]], dtype=torch.float64)
+    beta, g = torch.tensor([[0.5], [1.0]], dtype=torch.float64), torch.tensor([[0.9], [0.5]], dtype=torch.float64)
+    o = plain.delta_rule(q, k, v, beta, g)
+    s1 = torch.outer(k[0, 0], 0.5 * v[0, 0])
+    assert torch.allclose(o[0, 0], s1.T @ q[0, 0])
+    s2 = 0.5 * s1
+    s2 = s2 + torch.outer(k[1, 0], v[1, 0] - s2.T @ k[1, 0])
+    assert torch.allclose(o[1, 0], s2.T @ q[1, 0]) and torch.allclose(s2.T @ k[1, 0], v[1, 0])      # beta 1: the key now reads its value
+
+
+def test_plain_convolution_is_causal_and_starts_from_zeros():
+    x = torch.arange(1.0, 6.0, dtype=torch.float64)[:, None]
+    w = torch.tensor([[0.0, 0.0, 1.0]])                          # only the current token
+    assert torch.allclose(plain.causal_conv_silu(x, w), plain.silu(x))
+    w = torch.tensor([[1.0, 0.0, 0.0]])                          # only the token two back
+    assert torch.allclose(plain.causal_conv_silu(x, w)[:, 0], plain.silu(torch.tensor([0.0, 0.0, 1.0, 2.0, 3.0], dtype=torch.float64)))
+
+
+def test_plain_experts_weigh_their_input():
+    raw = plain.make_config([DEL])
+    t = {k: v.double() for k, v in plain.random_tensors(raw, 3).items()}
+    h = torch.randn(6, 64, dtype=torch.float64, generator=torch.Generator().manual_seed(1))
+    idx, w = plain.routed_choice(h, t, "l0.mlp.", 2)
+    s = torch.sigmoid(h @ t["l0.mlp.router"].T)
+    assert torch.equal(idx, s.topk(2).indices) and torch.allclose(w, s.topk(2).values)
+    want = torch.stack([sum(plain.expert(w[r, c] * h[r], t, f"l0.mlp.e{int(idx[r, c])}.") for c in range(2))
+                        + plain.expert(h[r], t, "l0.mlp.shared.") for r in range(6)])
+    assert torch.allclose(plain.moe(h, raw["layers"][0]["mlp"], t, "l0.mlp."), want)
+
+
+# --- every mechanism alone ------------------------------------------------------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(ALONE))
+def test_one_mechanism_alone(name, dtype, folders):
+    folder, raw, tensors = folders(name, ALONE[name], seed=11)
+    toks = tokens_for(raw, 75, 5)
+    eng = make_engine(folder, dtype)
+    check_request(eng, raw, tensors, toks, [75], dtype, f"{name} whole")
+    check_request(eng, raw, tensors, toks, [17, 2, 1, 1, 16, 3, 1, 1, 1, 2, 20, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1], dtype, f"{name} in portions")
+
+
+@pytest.mark.gpu
+def test_layers_agree_with_plain_one_by_one(folders):
+    """The residual stream after every layer (float32), with the pending update closed and added."""
+    from edgerag_b200.engine.step import StepEntry
+    from edgerag_b200.parts.base import settle_update
+
+    folder, raw, tensors = folders("full", FULL, seed=1)
+    toks = tokens_for(raw, 50, 2)
+    _, want = plain.forward(raw, tensors, toks, return_layers=True)
+    eng = make_engine(folder, "float32")
+    r, model = eng.runner, eng.model
+    r.admit("x")
+    ctx, ordered = r.prepare([StepEntry("x", tokens=toks, want=[])])
+    hidden = ctx.buf("model.hidden", (len(toks), model.hidden_size), torch.float32)
+    model.embedding.forward(ctx, hidden)
+    delta = None
+    for run, call in enumerate(model.schedule):
+        delta = model.blocks[call.layer].forward(hidden, delta, ctx, call)
+        settle_update(hidden, delta, model.dtype)
+        delta = None
+        err = (hidden.cpu().double() - want[run]).abs().max() / want[run].abs().max()
+        assert err < 5e-5, f"layer {call.layer}: {err:.2e}"
+    r.finish(ordered)
+
+
+# --- the whole model: prompts, decoding, portions, batches ------------------------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefill_decoding_and_portions_agree_with_plain(dtype, folders):
+    folder, raw, tensors = folders("full", FULL, seed=1)
+    toks = tokens_for(raw, 150, 6)
+    eng = make_engine(folder, dtype)
+    for rid, cuts in (("whole", [150]), ("decode", [40] + [1] * 110), ("chunks", [2, 31, 2, 16, 15, 1, 2, 33, 3, 2, 2, 17] + [1] * 30),
+                      ("pairs", [2] * 75)):
+        check_request(eng, raw, tensors, toks, cuts, dtype, rid)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("page", [4, 64])
+def test_other_page_sizes(page, folders):
+    folder, raw, tensors = folders("full", FULL, seed=1)
+    toks = tokens_for(raw, 90, 8)
+    eng = make_engine(folder, "float32", block_size=page, num_blocks=256 // page)
+    check_request(eng, raw, tensors, toks, [33, 2, 1, 1, 19] + [1] * 34, "float32", f"pages of {page}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unequal_requests_in_one_batch_equal_each_alone(dtype, folders):
+    """Portions of some requests beside single tokens of others; a request pauses for a step; requests end and their
+    pages and state slots go to new ones (four slots, six requests, freed pages poisoned).  A slot that is used again
+    must start from zeros: a state left behind by the request before shows in the first rows."""
+    from edgerag_b200.engine.step import StepEntry
+
+    folder, raw, tensors = folders("full", FULL, seed=1)
+    lens = {"a": 70, "b": 33, "c": 1, "d": 90, "e": 18, "f": 47}
+    toks = {k: tokens_for(raw, n, 20 + i) for i, (k, n) in enumerate(lens.items())}
+    eng = make_engine(folder, dtype, num_blocks=14)       # 224 tokens of pages: never room for all at once
+    r = eng.runner
+    plan = [
+        [("a", 30), ("b", 2)], [("a", 1), ("b", 16), ("c", 1)], [("a", 17), ("b", 1)], [("b", 14), ("d", 40), ("a", 1)],
+        [("a", 21), ("d", 1)], [("d", 33), ("e", 2)], [("d", 16), ("e", 1), ("f", 3)], [("e", 15), ("f", 1)], [("f", 43)],
+    ]
+    fed = {k: 0 for k in lens}
+    got = {k: [] for k in lens}
+    picks = {k: [] for k in lens}
+    slots_seen = {}
+    for step in plan:
+        entries = []
+        for rid, n in step:
+            if fed[rid] == 0:
+                r.admit(rid)
+                slots_seen[rid] = eng.cache.requests[rid].slot
+            entries.append(StepEntry(rid, tokens=toks[rid][fed[rid]: fed[rid] + n], want=list(range(n))))
+        eng.log.new_step()
+        first_row, row = {}, 0                               # the runner puts single tokens first: every entry's rows in the step
+        for rid, n in sorted(step, key=lambda e: e[1] != 1):
+            first_row[rid] = row
+            row += n
+        out = r.step(entries).float().cpu()
+        row = 0
+        for rid, n in step:
+            got[rid].append(out[row: row + n].clone())
+            picks[rid].append((len(eng.log.steps) - 1, first_row[rid], n))
+            row += n
+            fed[rid] += n
+            if fed[rid] == lens[rid]:
+                r.release(rid)
+        eng.cache.check_invariants()
+    assert fed == lens
+    assert len(set(slots_seen.values())) < len(lens), "no state slot was used twice"
+    for rid in lens:
+        chosen = eng.log.of_rows(picks[rid]) if dtype == "bfloat16" else None
+        assert_close(torch.cat(got[rid]), plain.forward(raw, tensors, toks[rid], chosen=chosen), dtype, f"request {rid}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_over_many_chunks(dtype, folders):
+    folder, raw, tensors = folders("full", FULL, seed=1)
+    toks = tokens_for(raw, 330, 9)
+    eng = make_engine(folder, dtype)
+    check_request(eng, raw, tensors, toks, [3] + [1] * 327, dtype, "330 tokens, 327 of them one by one")
+
+
+@pytest.mark.gpu
+def test_layer_sizes_of_a_larger_model(folders):
+    """Heads of 64 and 128, a chunk longer than a split of keys, a prompt of several chunks, experts of more rows than a tile."""
+    raw = plain.make_config([plain.delta_layer(heads=4, kv_heads=2, dim=64, vdim=128, conv=4, experts=8, top=2, ff=64, shared_ff=128),
+                             plain.attention_layer(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=32, base=250000.0, size=600, scale=0.125,
+                                                   experts=4, top=1, ff=96, shared_ff=64),
+                             plain.attention_layer(heads=2, kv_heads=1, dim=128, vdim=128, rot_dims=64, size=256, scale=0.09, experts=None)],
+                            width=128, vocab=96)
+    folder, raw, tensors = folders("larger", raw, seed=3)
+    toks = tokens_for(raw, 1300, 9)
+    eng = make_engine(folder, "float32", num_blocks=256, max_step_tokens=2048)
+    check_request(eng, raw, tensors, toks, [1300], "float32", "whole")
+    check_request(eng, raw, tensors, toks, [590, 2, 9, 257, 400, 30] + [1] * 12, "float32", "portions")
+
+
+# --- kernels with inputs made so that a fault shows ---------------------------------------------------
+
+def _chunk_reference(q, keys, values, where, scale, chunk, rep):
+    """Plain attention under a mask of chunks: q [n, H, d] float64; keys/values[seq] [len, G, d]; where[t] = (seq, position)."""
+    out = torch.zeros(q.shape[0], q.shape[1], values[0].shape[-1], dtype=torch.float64)
+    for t, (seq, pos) in enumerate(where):
+        see = [j for j in range(pos + 1) if chunk <= 0 or j // chunk == pos // chunk]
+        for h in range(q.shape[1]):
+            s = keys[seq][see, h // rep] @ q[t, h] * scale
+            out[t, h] = torch.softmax(s, 0) @ values[seq][see, h // rep]
+    return out
+
+
+def _paged(rows, page_size, dtype, shuffle_seed=0):
+    """Scatter each sequence's rows [len, G, d] over shuffled pages; unused slots hold NaN.  (pages [P, G, page, d], tables)."""
+    G, d = rows[0].shape[1:]
+    need = [-(-r.shape[0] // page_size) for r in rows]
+    order = torch.randperm(sum(need) + 3, generator=torch.Generator().manual_seed(shuffle_seed)).tolist()
+    pages = torch.full((sum(need) + 3, G, page_size, d), float("nan"), dtype=torch.float64)
+    tables = torch.zeros(len(rows), max(need), dtype=torch.int32)
+    for s, r in enumerate(rows):
+        for i in range(need[s]):
+            page = order.pop()
+            tables[s, i] = page
+            part = r[i * page_size: (i + 1) * page_size]
+            pages[page, :, : part.shape[0]] = part.transpose(0, 1)
+    return pages.to(dtype).cuda(), tables.cuda()
+
+
+CHUNK_CASES = [  # (heads, kv heads, head size, page, chunk)
+    (4, 2, 32, 16, 24), (6, 1, 48, 8, 17), (2, 2, 64, 16, 64), (8, 2, 128, 32, 40), (3, 3, 16, 16, 9), (4, 2, 24, 16, 1),
+    (6, 2, 64, 8, 100), (8, 2, 64, 16, 33), (4, 1, 64, 32, 130), (4, 4, 64, 64, 128), (2, 1, 64, 16, 0),
+]
+
+
+def _dominant_queries(case, lens, seed):
+    """Queries that each look for one key: at their chunk's first position and the one before it, at a page's last and
+    first slot, far back, at position 0 and at their own.  -> q [n, H, d], keys, values, [(sequence, position)]"""
+    H, G, d, page, chunk = case
+    g = torch.Generator().manual_seed(seed)
+    keys = [torch.randn(n, G, d, generator=g, dtype=torch.float64) * 0.3 for n in lens]
+    values = [torch.randn(n, G, d, generator=g, dtype=torch.float64) for n in lens]
+    c = chunk or 50
+    queries, where = [], []
+    for s, n in enumerate(lens):
+        for pos in sorted({n - 1, n - 2, c, c - 1, c + 1, 2 * c - 1, 2 * c, (n // c) * c, (n // c) * c - 1, page - 1, page, 2 * page, 0, 1,
+                           n // 2}):
+            if not 0 <= pos < n:
+                continue
+            first = pos - pos % c
+            for target in (first, first - 1, first + 1, (pos // page) * page - 1, (pos // page) * page, 0, 1, pos, pos - 1, pos - c,
+                           pos - c + 1):
+                if 0 <= target <= pos:
+                    q = torch.randn(H, d, generator=g, dtype=torch.float64) * 0.3
+                    for h in range(H):                      # the target's key, scaled up, is what the query looks for
+                        kk = keys[s][target, h // (H // G)]
+                        q[h] += 12.0 * kk / kk.norm() ** 2
+                    queries.append(q)
+                    where.append((s, pos))
+    return torch.stack(queries), keys, values, where
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", CHUNK_CASES)
+def test_chunk_attention_with_one_key_made_dominant(case, dtype):
+    """A kernel that reads a key of the chunk before, skips its chunk's first key or stops at a page's border returns
+    another value row.  Rows of prompts, single tokens in splits of two sizes, and the tensor-core kernel for portions."""
+    from edgerag_b200.ops import kernels as k
+
+    H, G, d, page, chunk = case
+    tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    lens = [150, 77, 2 * (chunk or 50) + 3, 300]
+    q, keys, values, where = _dominant_queries(case, lens, H * 100 + d + chunk)
+    if dtype == "bfloat16":
+        q, keys, values = q.to(tdt).double(), [x.to(tdt).double() for x in keys], [x.to(tdt).double() for x in values]
+    want = _chunk_reference(q, keys, values, where, 0.5, chunk, H // G)
+    # the test's own sharpness: with a chunk one position longer the answers differ clearly
+    if chunk:
+        other = _chunk_reference(q, keys, values, where, 0.5, chunk + 1, H // G)
+        assert (other - want).abs().amax((1, 2)).max() > 0.3
+    kp, tables = _paged(keys, page, tdt, 1)
+    vp, _ = _paged(values, page, tdt, 1)
+    n = q.shape[0]
+    qd = q.reshape(n, H * d).to(tdt).cuda()
+    seq_of = torch.tensor([s for s, _ in where], dtype=torch.int32).cuda()
+    pos = torch.tensor([p for _, p in where], dtype=torch.int32).cuda()
+    tol = 2e-5 if dtype == "float32" else 2e-2
+
+    def check(out, what):
+        err = (out.double().cpu().reshape(n, H, d) - want).abs().amax((1, 2))
+        assert err.max() < tol, f"{what}: query {int(err.argmax())} at {where[int(err.argmax())]}: {err.max():.2e}"
+
+    out = torch.full_like(qd, float("nan"))
+    k.attention_rows(qd, kp, vp, tables, seq_of, pos, out, H, 0.5, chunk=chunk)
+    check(out, "rows")
+    tables1 = tables[seq_of.long()].contiguous()               # every query a sequence of its own
+    tok = torch.arange(n, dtype=torch.int32).cuda()
+    for split in (16, 64):
+        if split % page and page % split:
+            continue
+        splits = (chunk or max(lens)) // split + 2
+        acc, ml = k.decode_scratch_floats(n, H, d, splits)
+        out1 = torch.full_like(qd, float("nan"))
+        k.attention_decode(qd, kp, vp, tables1, tok, pos, out1, H, 0.5, torch.empty(acc, device="cuda"), torch.empty(ml, device="cuda"),
+                           splits, split_keys=split, chunk=chunk)
+        check(out1, f"single tokens, splits of {split}")
+    if k.prefill_tc_supported(tdt, d, 0, page):
+        out2 = torch.full_like(qd, float("nan"))
+        starts = torch.arange(n + 1, dtype=torch.int32).cuda()
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        k.attention_prefill_tc(qd, kp, vp, tables1, starts, pos, out2, n, H, 0.5, status, chunk=chunk)
+        assert int(status.item()) == 0
+        check(out2, "tensor cores, portions of one row")
+
+
+CHUNK_PORTIONS = [  # (page, chunk, [(past, new tokens)])
+    (16, 100, [(0, 700)]), (16, 128, [(0, 300), (517, 260)]), (8, 129, [(40, 530)]), (64, 300, [(1000, 2), (3, 900)]),
+    (16, 257, [(0, 1030)]), (32, 40, [(2100, 200), (0, 31)]), (128, 1, [(5, 300)]), (16, 640, [(777, 513)]), (16, 64, [(63, 2), (64, 130)]),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", CHUNK_PORTIONS)
+def test_chunk_attention_of_portions_on_tensor_cores(case):
+    """Portions of prompts behind pasts of several lengths (bfloat16, heads of 64): every row looks for one key, in turn
+    the first of its chunk, the last of the chunk before, its own, the one before and the sequence's first."""
+    from edgerag_b200.ops import kernels as k
+
+    page, chunk, portions = case
+    H, G, d = 4, 2, 64
+    g = torch.Generator().manual_seed(page + chunk)
+    lens = [past + new for past, new in portions]
+    bf = lambda x: x.to(torch.bfloat16).double()                  # noqa: E731
+    keys = [bf(torch.randn(n, G, d, generator=g, dtype=torch.float64) * 0.3) for n in lens]
+    values = [bf(torch.randn(n, G, d, generator=g, dtype=torch.float64)) for n in lens]
+    queries, where = [], []
+    for s, (past, new) in enumerate(portions):
+        for i in range(new):
+            pos = past + i
+            first = pos - pos % chunk
+            target = (first, first - 1, pos, pos - 1, 0, first + 1)[i % 6]
+            target = min(max(target, 0), pos)
+            q = torch.randn(H, d, generator=g, dtype=torch.float64) * 0.3
+            for h in range(H):
+                kk = keys[s][target, h // (H // G)]
+                q[h] += 12.0 * kk / kk.norm() ** 2
+            queries.append(q)
+            where.append((s, pos))
+    q = bf(torch.stack(queries))
+    want = _chunk_reference(q, keys, values, where, 0.5, chunk, H // G)
+    kp, tables = _paged(keys, page, torch.bfloat16, 2)
+    vp, _ = _paged(values, page, torch.bfloat16, 2)
+    n = q.shape[0]
+    qd = q.reshape(n, H * d).to(torch.bfloat16).cuda()
+    pos = torch.tensor([p for _, p in where], dtype=torch.int32).cuda()
+    starts = torch.tensor([0] + list(np.cumsum([new for _, new in portions])), dtype=torch.int32).cuda()
+    blocks = k.prefill_tc_blocks([new for _, new in portions])
+    for ranges in (1, 3):
+        out = torch.full_like(qd, float("nan"))
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        part_o = part_ml = None
+        if ranges > 1:
+            no, nm = k.prefill_tc_scratch_floats(n, H, ranges)
+            part_o, part_ml = torch.empty(no, device="cuda"), torch.empty(nm, device="cuda")
+        k.attention_prefill_tc(qd, kp, vp, tables, starts, pos, out, blocks, H, 0.5, status, key_splits=ranges, part_o=part_o,
+                               part_ml=part_ml, chunk=chunk)
+        assert int(status.item()) == 0
+        err = (out.double().cpu().reshape(n, H, d) - want).abs().amax((1, 2))
+        assert err.max() < 2e-2, f"{ranges} key ranges: row {int(err.argmax())} at {where[int(err.argmax())]}: {err.max():.2e}"
+
+
+def _delta_rows(n, H, G, d, dv, g, tdt, b_shift=0.0, a_shift=0.0):
+    """Random activated rows q | k | v and a projection holding the raw b and a columns behind 5 columns of filler."""
+    qkv = (torch.randn(n, 2 * G * d + H * dv, generator=g) * 0.7).to(tdt)
+    proj = torch.randn(n, 5 + 2 * H + 3, generator=g)
+    proj[:, 5: 5 + H] += b_shift
+    proj[:, 5 + H: 5 + 2 * H] += a_shift
+    return qkv, proj.to(tdt)
+
+
+def _delta_plain(qkv, proj, H, G, d, dv, dt_bias, a_log):
+    n = qkv.shape[0]
+    x = qkv.double()
+    q = plain.unit_vectors(x[:, : G * d].view(n, G, d)) * d ** -0.5
+    k = plain.unit_vectors(x[:, G * d: 2 * G * d].view(n, G, d))
+    v = x[:, 2 * G * d:].view(n, H, dv)
+    beta = torch.sigmoid(proj.double()[:, 5: 5 + H])
+    gate = torch.exp(-torch.exp(a_log.double()) * plain.softplus(proj.double()[:, 5 + H: 5 + 2 * H] + dt_bias.double()))
+    return plain.delta_rule(q.repeat_interleave(H // G, 1), k.repeat_interleave(H // G, 1), v, beta, gate).reshape(n, H * dv)
+
+
+DELTA_CASES = [(4, 2, 16, 24), (3, 3, 40, 8), (6, 1, 24, 40), (2, 1, 128, 128), (4, 2, 64, 96), (1, 1, 200, 5), (5, 5, 7, 300)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", DELTA_CASES)
+def test_delta_scan_in_portions_and_slots(case, dtype):
+    """Three requests of unequal lengths scanned whole, and again in unequal portions over several launches with their
+    slots in another order: the same outputs, and the plain rule's."""
+    from edgerag_b200.ops import kernels as k
+
+    H, G, d, dv = case
+    tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    g = torch.Generator().manual_seed(H * 1000 + d)
+    lens = [70, 1, 33]
+    dt_bias, a_log = torch.randn(H, generator=g) - 1.0, torch.log(0.3 + 2 * torch.rand(H, generator=g))
+    rows = [_delta_rows(n, H, G, d, dv, g, tdt) for n in lens]
+    want = [_delta_plain(qkv, proj, H, G, d, dv, dt_bias, a_log) for qkv, proj in rows]
+
+    def run(plan, slots):
+        state = torch.zeros(5, H, dv, d, device="cuda")
+        state[3] = float("nan")                                    # a slot nobody uses must not be read
+        fed = [0] * len(lens)
+        got = [[] for _ in lens]
+        for step in plan:
+            qkv = torch.cat([rows[s][0][fed[s]: fed[s] + n] for s, n in step]).cuda()
+            proj = torch.cat([rows[s][1][fed[s]: fed[s] + n] for s, n in step]).cuda()
+            starts = torch.tensor([0] + list(np.cumsum([n for _, n in step])), dtype=torch.int32).cuda()
+            sl = torch.tensor([slots[s] for s, _ in step], dtype=torch.int32).cuda()
+            out = torch.full((qkv.shape[0], H * dv), float("nan"), device="cuda")
+            k.delta_scan(qkv, proj, 5, 5 + H, dt_bias.cuda(), a_log.cuda(), state, len(step), starts, sl, out, G, d)
+            row = 0
+            for s, n in step:
+                got[s].append(out[row: row + n].cpu())
+                row += n
+                fed[s] += n
+        assert fed == lens
+        return [torch.cat(x) for x in got], state.cpu()
+
+    whole, state_a = run([[(0, 70), (1, 1), (2, 33)]], [0, 1, 2])
+    cut, state_b = run([[(0, 17), (2, 2)], [(2, 1), (0, 1)], [(0, 2), (1, 1), (2, 30)], [(0, 50)]], [4, 0, 2])
+    tol = 3e-5 if dtype == "float32" else 3e-5                    # the scan itself is float whatever the rows' type
+    for s in range(3):
+        assert (whole[s].double() - want[s]).abs().max() < tol * max(1.0, want[s].abs().max()), f"request {s} whole"
+        assert (cut[s].double() - want[s]).abs().max() < tol * max(1.0, want[s].abs().max()), f"request {s} in portions"
+    assert torch.allclose(state_a[0], state_b[4], atol=1e-5) and torch.allclose(state_a[2], state_b[2], atol=1e-5)
+    assert torch.isnan(state_a[3]).all()
+
+
+@pytest.mark.gpu
+def test_delta_state_keeps_a_far_write_and_a_strong_write_replaces():
+    """Decays of almost 1 and keys that are orthogonal: a value written at the first token is read back 400 tokens
+    later (a state that is lost, reset at a launch's border or decayed twice does not return it); a second write with
+    the same key and write strength 1 replaces it."""
+    from edgerag_b200.ops import kernels as k
+
+    H = G = 1
+    d, dv, n = 64, 32, 401
+    g = torch.Generator().manual_seed(5)
+    basis = torch.linalg.qr(torch.randn(d, d, generator=g)).Q            # orthonormal keys
+    qkv = torch.zeros(n, 2 * d + dv)
+    proj = torch.zeros(n, 2)
+    for t in range(n):
+        qkv[t, d: 2 * d] = basis[1 + t % (d - 1)]                          # keys that never equal basis[0] again ...
+        qkv[t, 2 * d:] = torch.randn(dv, generator=g)
+        qkv[t, :d] = basis[1 + (t + 7) % (d - 1)]
+    v0 = torch.randn(dv, generator=g)
+    qkv[0, d: 2 * d], qkv[0, 2 * d:] = basis[0], v0
+    qkv[400, :d] = basis[0] * 3.0                                          # ... until the last token asks for it (any length: unit vectors)
+    proj[:, 0] = 30.0                                                       # beta = 1
+    proj[:, 1] = -30.0                                                      # softplus(-30) ~ 1e-13: g = 1
+    args = (torch.zeros(1).cuda(), torch.zeros(1).cuda())
+    want = _delta_plain_simple(qkv, proj, d, dv)
+    assert (want[400] - v0.double() * d ** -0.5).abs().max() < 1e-3, "the test's inputs do not bring the first value back"
+    for cuts in ([401], [1] * 401, [100, 2, 298, 1], [399, 2]):
+        state = torch.zeros(1, 1, dv, d, device="cuda")
+        outs, at = [], 0
+        for c in cuts:
+            out = torch.empty(c, dv, device="cuda")
+            k.delta_scan(qkv[at: at + c].cuda(), proj[at: at + c].cuda(), 0, 1, *args, state, 1,
+                         torch.tensor([0, c], dtype=torch.int32).cuda(), torch.zeros(1, dtype=torch.int32).cuda(), out, 1, d)
+            outs.append(out.cpu())
+            at += c
+        got = torch.cat(outs).double()
+        assert (got - want).abs().max() < 1e-4, f"cuts {cuts[:4]}"
+    # a second write along the first key with strength 1 replaces the value there
+    qkv2 = qkv.clone()
+    v1 = torch.randn(dv, generator=g)
+    qkv2[200, d: 2 * d], qkv2[200, 2 * d:] = basis[0] * 0.5, v1
+    want2 = _delta_plain_simple(qkv2, proj, d, dv)
+    assert (want2[400] - v1.double() * d ** -0.5).abs().max() < 1e-3
+    state = torch.zeros(1, 1, dv, d, device="cuda")
+    out = torch.empty(n, dv, device="cuda")
+    k.delta_scan(qkv2.cuda(), proj.cuda(), 0, 1, *args, state, 1, torch.tensor([0, n], dtype=torch.int32).cuda(),
+                 torch.zeros(1, dtype=torch.int32).cuda(), out, 1, d)
+    assert (out.cpu().double() - want2).abs().max() < 1e-4
+
+
+def _delta_plain_simple(qkv, proj, d, dv):
+    n = qkv.shape[0]
+    x = qkv.double()
+    q = plain.unit_vectors(x[:, :d].view(n, 1, d)) * d ** -0.5
+    kk = plain.unit_vectors(x[:, d: 2 * d].view(n, 1, d))
+    beta = torch.sigmoid(proj.double()[:, :1])
+    gate = torch.exp(-plain.softplus(proj.double()[:, 1:2]))               # A_log = 0, dt_bias = 0
+    return plain.delta_rule(q, kk, x[:, 2 * d:].view(n, 1, dv), beta, gate).reshape(n, dv)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_convolution_continues_from_its_record(dtype):
+    """The convolution of q | k | v without a bias: whole against portions of one and two tokens, from a record of zeros."""
+    from edgerag_b200.ops import kernels as k
+
+    tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    g = torch.Generator().manual_seed(3)
+    for taps, channels in ((4, 40), (2, 24), (3, 72), (7, 8)):
+        x = torch.randn(29, channels + 6, generator=g).to(tdt)
+        w = (torch.randn(channels, taps, generator=g) * 0.6).to(tdt)
+        want = plain.causal_conv_silu(x[:, 3: 3 + channels].double(), w.double())
+        state = torch.full((3, taps - 1, channels), float("nan"), device="cuda")
+        state[2] = 0
+        at, outs = 0, []
+        for c in (1, 2, 1, 1, 9, 2, 13):
+            rows = x[at: at + c].cuda()
+            out = torch.empty(c, channels, dtype=tdt, device="cuda")
+            seq_of, starts = torch.zeros(c, dtype=torch.int32).cuda(), torch.tensor([0, c], dtype=torch.int32).cuda()
+            slot = torch.tensor([2], dtype=torch.int32).cuda()
+            k.conv_silu(rows, 3, w.cuda(), None, state, seq_of, starts, slot, out)
+            k.conv_state_update(rows, 3, state, 1, starts, slot)
+            outs.append(out.cpu())
+            at += c
+        err = (torch.cat(outs).double() - want).abs().max()
+        assert err < (1e-5 if dtype == "float32" else 3e-2), f"{taps} taps: {err:.2e}"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_head_norm_and_gate(dtype):
+    from edgerag_b200.ops import kernels as k
+
+    tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    g = torch.Generator().manual_seed(8)
+    for H, dv in ((4, 24), (1, 128), (6, 40), (3, 5), (2, 300)):
+        o = torch.randn(11, H * dv, generator=g) * 3.0
+        o[2] *= 1e-4                                               # a row where eps matters
+        wide = torch.randn(11, H * dv + 9, generator=g).to(tdt)
+        w = 1 + 0.3 * torch.randn(dv, generator=g)
+        out = torch.empty(11, H * dv, dtype=tdt, device="cuda")
+        k.head_norm_gate(o.cuda(), wide.cuda()[:, 4: 4 + H * dv], w.cuda(), out, H, 1e-5)
+        od = o.double().view(11, H, dv)
+        want = od / torch.sqrt((od * od).mean(-1, keepdim=True) + 1e-5) * w.double() * plain.silu(wide[:, 4: 4 + H * dv].double().view(11, H, dv))
+        err = (out.cpu().double().view(11, H, dv) - want).abs().max()
+        assert err < (2e-5 if dtype == "float32" else 4e-2), f"{H} heads of {dv}: {err:.2e}"
+
+
+MOE_CASES = [  # (tokens, width, ff, experts, top)
+    (1, 64, 48, 4, 2), (7, 80, 24, 3, 3), (50, 72, 40, 5, 1), (130, 64, 136, 8, 2), (33, 128, 200, 16, 4), (3, 40, 8, 2, 1),
+    (300, 256, 192, 6, 2),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", MOE_CASES)
+def test_routed_experts_kernels(case, dtype):
+    """The router's choices and scores, the lists made on the device, and the two products against the plain experts."""
+    from edgerag_b200.ops import kernels as k
+
+    n, width, ff, E, top = case
+    tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    g = torch.Generator().manual_seed(n + E)
+    x = torch.randn(n, width + 8, generator=g).to(tdt)[:, 8:]                 # a view with a row stride
+    t = {"router": (torch.randn(E, width, generator=g) * 3 / math.sqrt(width)).to(torch.bfloat16).float()}
+    for e in range(E):
+        t[f"e{e}.gate"] = (torch.randn(ff, width, generator=g) / math.sqrt(width)).to(tdt)
+        t[f"e{e}.up"] = (torch.randn(ff, width, generator=g) / math.sqrt(width)).to(tdt)
+        t[f"e{e}.down"] = (torch.randn(width, ff, generator=g) / math.sqrt(ff)).to(tdt)
+    if E >= 5:
+        t["router"][2] = t["router"][1]                                             # a tie: the lower index wins
+    xd = x.cuda()
+    lists = torch.full((k.moe_lists_ints(n, E, top),), -7, dtype=torch.int32, device="cuda")
+    score = torch.empty(n * top, device="cuda")
+    k.moe_route(xd, t["router"].cuda(), top, lists, score)
+    z = x.double() @ t["router"].double().T
+    pairs = n * top
+    choice = lists[:pairs].cpu().view(n, top).long()
+    order = lists[pairs: 2 * pairs].cpu().long()
+    counts, offsets = (lists[2 * pairs + i * (E + 1): 2 * pairs + (i + 1) * (E + 1)].cpu().long() for i in range(2))
+    # the choices: the largest logits in falling order; a close call may differ, a clear one may not
+    zs = torch.sort(z, dim=-1, descending=True).values
+    for r in range(n):
+        assert len(set(choice[r].tolist())) == top
+        for c in range(top):
+            assert z[r, choice[r, c]] >= zs[r, c] - 1e-4, f"row {r} choice {c}"
+    if E >= 5:
+        assert not ((choice == 2).any(-1) & ~(choice == 1).any(-1)).any(), "of two equal experts the higher index was chosen alone"
+    assert torch.allclose(score.cpu().double().view(n, top), torch.sigmoid(torch.gather(z, 1, choice)), atol=1e-5)
+    # the lists: every pair once, behind its expert's offset, in rising order
+    assert counts[:E].tolist() == [int((choice == e).sum()) for e in range(E)]
+    assert offsets.tolist() == [0] + list(np.cumsum(counts[:E].tolist()))
+    for e in range(E):
+        mine = order[offsets[e]: offsets[e + 1]]
+        assert mine.tolist() == sorted(mine.tolist()) and all(int(choice.view(-1)[p]) == e for p in mine)
+    # the products
+    act = torch.full((pairs, ff), float("nan"), dtype=tdt, device="cuda")
+    w_gate_up = torch.stack([torch.cat([t[f"e{e}.gate"], t[f"e{e}.up"]], 0) for e in range(E)]).cuda()
+    w_down = torch.stack([t[f"e{e}.down"] for e in range(E)]).cuda()
+    k.moe_gate_up(xd, w_gate_up, lists, score, top, act)
+    parts = torch.full((top + 1, n, width), float("nan"), device="cuda")
+    k.moe_down(act, w_down, lists, top, parts)
+    got = parts[:top].sum(0).cpu().double()
+    sc = score.cpu().view(n, top)
+    want = torch.zeros(n, width, dtype=torch.float64)
+    for r in range(n):
+        for c in range(top):
+            scaled = (sc[r, c] * x[r].float()).to(tdt)                              # the expert's input, rounded once
+            want[r] += plain.expert(scaled.double()[None], {kk: v.double() for kk, v in t.items()}, f"e{int(choice[r, c])}.")[0]
+    err = (got - want).abs().max() / want.abs().max()
+    assert err < (2e-5 if dtype == "float32" else 2e-2), f"{err:.2e}"
+    assert torch.isnan(parts[top]).all(), "the shared expert's part was written"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_an_expert_does_not_depend_on_the_other_rows(dtype):
+    """A token's update is the same bits alone, among 5 and among 200 tokens (the products walk k in one order)."""
+    from edgerag_b200.ops import kernels as k
+
+    tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    g = torch.Generator().manual_seed(2)
+    width, ff, E, top = 96, 72, 6, 2
+    x = torch.randn(200, width, generator=g).to(tdt).cuda()
+    router = (torch.randn(E, width, generator=g) / 3).cuda()
+    wgu = (torch.randn(E, 2 * ff, width, generator=g) / 10).to(tdt).cuda()
+    wd = (torch.randn(E, width, ff, generator=g) / 10).to(tdt).cuda()
+
+    def run(rows):
+        n = rows.shape[0]
+        lists = torch.empty(k.moe_lists_ints(n, E, top), dtype=torch.int32, device="cuda")
+        score = torch.empty(n * top, device="cuda")
+        k.moe_route(rows, router, top, lists, score)
+        act = torch.empty(n * top, ff, dtype=tdt, device="cuda")
+        k.moe_gate_up(rows, wgu, lists, score, top, act)
+        parts = torch.empty(top, n, width, device="cuda")
+        k.moe_down(act, wd, lists, top, parts)
+        return parts.cpu()
+
+    big = run(x)
+    assert torch.equal(run(x[17:18])[:, 0], big[:, 17])
+    assert torch.equal(run(x[15:20])[:, 2], big[:, 17])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_over_the_whole_projection_with_rotation_and_cache_write(dtype):
+    """Biases, the unit-RMS norm over all of a token's query entries (and key entries) at once, the turn of the halves
+    of the first entries of every head, and the write of keys and values to the tokens' cache slots."""
+    from edgerag_b200.ops import kernels as k
+
+    tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    g = torch.Generator().manual_seed(4)
+    for H, G, d, rot, page in ((4, 2, 32, 12, 16), (3, 3, 24, 24, 8), (6, 1, 48, 0, 16), (2, 1, 64, 32, 4)):
+        n, eps = 9, 1e-5
+        qw, kw = H * d, G * d
+        qkv = torch.randn(n, qw + 2 * kw + 3, generator=g).to(tdt)
+        qb, kb, vb = torch.randn(qw, generator=g), torch.randn(kw, generator=g), torch.randn(kw, generator=g)
+        qn, kn = 1 + 0.2 * torch.randn(qw, generator=g), 1 + 0.2 * torch.randn(kw, generator=g)
+        pos = torch.tensor([0, 1, 5, 17, 400, 3, 3, 99, 2], dtype=torch.int32)
+        slots = torch.tensor([7, 3, 20, 21, 0, 9, 40, 41, 13], dtype=torch.int32)
+        base = 700.0
+        inv = torch.tensor([base ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32) if rot else None
+        kp = torch.full((4 * 16 // page + 1, G, page, d), float("nan"), dtype=tdt, device="cuda")
+        vp = torch.full_like(kp, float("nan"))
+        dev = qkv.cuda()
+        k.qkv_whole_norm(dev, pos.cuda(), H, G, d, q_count=qw, k_count=kw, eps=eps, q_bias=qb.cuda(), k_bias=kb.cuda(), v_bias=vb.cuda(),
+                         q_norm=qn.cuda(), k_norm=kn.cuda(), inv_freq=None if inv is None else inv.cuda(), rot_dim=rot, slots=slots.cuda(),
+                         k_pages=kp, v_pages=vp, page_size=page)
+        x = qkv.double()
+        q = plain.rotate_halves(plain.rms_norm(x[:, :qw] + qb.double(), qn, eps).view(n, H, d), pos, base, rot)
+        kk = plain.rotate_halves(plain.rms_norm(x[:, qw: qw + kw] + kb.double(), kn, eps).view(n, G, d), pos, base, rot)
+        v = (x[:, qw + kw: qw + 2 * kw] + vb.double()).view(n, G, d)
+        tol = 6e-5 if dtype == "float32" else 4e-2          # (an angle of 400 turns in float: half a unit in the last place is 1.5e-5)
+        assert (dev[:, :qw].cpu().double().view(n, H, d) - q).abs().max() < tol
+        for t in range(n):
+            page_i, off = int(slots[t]) // page, int(slots[t]) % page
+            assert (kp[page_i, :, off].cpu().double() - kk[t]).abs().max() < tol, f"key of token {t}"
+            assert (vp[page_i, :, off].cpu().double() - v[t]).abs().max() < tol, f"value of token {t}"
+        assert int(torch.isfinite(kp[:, 0, :, 0]).sum()) == n, "slots of other tokens were written"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_residual_add_of_a_normed_update(dtype):
+    """x += rms(update) * w with eps inside the root, the update given as rows or as float partial sums, the stream float."""
+    from edgerag_b200.ops import kernels as k
+
+    tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    g = torch.Generator().manual_seed(6)
+    n, h, eps = 13, 88, 1e-5
+    hidden = torch.randn(n, h, generator=g) * 4
+    w = 1 + 0.2 * torch.randn(h, generator=g)
+    rows = (torch.randn(n, h, generator=g) * 0.01).to(tdt)           # small: eps matters
+    parts = torch.randn(3, n, h, generator=g)
+    bias = torch.randn(h, generator=g)
+    for delta, b in ((rows, None), (parts, None), (rows, bias)):
+        hd = hidden.clone().cuda()
+        out = torch.empty(n, h, dtype=tdt, device="cuda")
+        k.rms_between(hd, out, delta=delta.cuda(), bias=None if b is None else b.cuda(), post=(w.cuda(), eps))
+        upd = delta.double() if delta.dim() == 2 else delta.double().sum(0).to(tdt).double() if dtype == "bfloat16" else delta.double().sum(0)
+        if b is not None:
+            upd = upd + b.double()
+        want = hidden.double() + plain.rms_norm(upd, w, eps)
+        assert (hd.cpu().double() - want).abs().max() < (2e-5 if dtype == "float32" else 3e-2)
+        assert (out.cpu().double() - want).abs().max() < (2e-5 if dtype == "float32" else 6e-2)
+
+
+# --- a model whose scores single out edge keys; a recurrence that has to remember ------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_model_whose_scores_single_out_keys_at_a_chunk_edge(dtype, folders):
+    """One attention layer with query and key weights scaled up: its softmax is sharp, and whether the token just before
+    a chunk's first one is seen decides rows.  The plain model with a chunk one longer must differ clearly (else the
+    weights do not test the edge), the engine must not."""
+    layer = plain.attention_layer(heads=4, kv_heads=2, dim=32, vdim=24, rot_dims=8, size=19, scale=1.5, experts=None)
+    raw = plain.make_config([layer], width=64, vocab=97)
+    folder, raw, tensors = folders("sharp", raw, seed=4)
+    toks = tokens_for(raw, 120, 3)
+    want = plain.forward(raw, tensors, toks)
+    for other in (18, 20):
+        moved = copy.deepcopy(raw)
+        moved["layers"][0]["mixer"]["mask"]["size"] = other
+        blind = plain.forward(moved, tensors, toks)
+        assert row_errors(blind[30:], want[30:]).max() > 0.5, f"the test's weights do not tell chunks of 19 from chunks of {other}"
+    eng = make_engine(folder, dtype)
+    for rid, cuts in (("whole", [120]), ("tail", [18] + [1] * 102), ("edges", [19, 19, 1, 18, 2, 17, 20, 1, 1, 1, 2, 19]),
+                      ("mixed", [3, 2, 14, 1, 1, 30, 2, 2, 1, 40] + [1] * 24)):
+        check_request(eng, raw, tensors, toks, cuts, dtype, rid)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_model_whose_recurrence_has_to_remember(dtype, folders):
+    """One delta layer with slow decays (A_log far below 0): what the first tokens wrote still shapes the rows of the
+    last ones, so a state that is dropped between portions, or a convolution record that is, shows.  The plain model
+    fed only the last 60 tokens must differ clearly from the one fed all."""
+    raw = plain.make_config([plain.delta_layer(heads=2, kv_heads=1, dim=32, vdim=48, conv=4, experts=None)], width=64, vocab=97)
+    def slow_and_weak(tensors):
+        tensors["l0.mix.A_log"] = torch.full_like(tensors["l0.mix.A_log"], -6.0)
+        tensors["l0.mix.b"] = tensors["l0.mix.b"] * 0.1                   # weak writes: old content stays
+
+    folder, raw, tensors = folders("remembers", raw, seed=9, edit=slow_and_weak)
+    toks = tokens_for(raw, 200, 3)
+    want = plain.forward(raw, tensors, toks)
+    forgot = plain.forward(raw, tensors, toks[140:])
+    e = row_errors(forgot[20:], want[160:])
+    assert e.min() > 0.05 and e.max() > 0.5, "the test's weights forget within 160 tokens"
+    eng = make_engine(folder, dtype)
+    for rid, cuts in (("whole", [200]), ("tail", [140] + [1] * 60), ("portions", [2, 3, 100, 1, 1, 2, 31, 2] + [1] * 58)):
+        check_request(eng, raw, tensors, toks, cuts, dtype, rid)
+
+
+# --- generation through the engine's own entry point -----------------------------------------------
+
+def plain_greedy(raw, tensors, prompt, n_new):
+    toks, margins = list(prompt), []
+    for _ in range(n_new):
+        last = plain.forward(raw, tensors, toks)[-1]
+        top = torch.topk(last, 2).values
+        margins.append(float(top[0] - top[1]))
+        toks.append(int(last.argmax()))
+    return toks[len(prompt):], margins
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,graphs", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+def test_greedy_generation_through_the_scheduler(dtype, graphs, folders):
+    """Five prompts through ``Engine.generate`` with two slots and portions of 8 tokens: the scheduler cuts prompts,
+    batches them with decoding requests and hands state slots and pages on.  float32: the tokens of the plain model
+    while its margins are clear.  bfloat16 (where a router's close call may change a token): every generated token is
+    the best one, or within a small margin of it, of the same engine fed the request alone in one step."""
+    from edgerag_b200.sampling.params import SamplingParams
+
+    folder, raw, tensors = folders("full", FULL, seed=1)
+    prompts = [tokens_for(raw, n, 40 + n) for n in (21, 3, 34, 9, 1)]
+    eng = make_engine(folder, dtype, max_batch_size=2, num_blocks=8, chunk_size=8, max_step_tokens=None, cuda_graphs=graphs)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=30))
+    eng.cache.check_invariants()
+    assert eng.cache.free_pages() == [8] * len(eng.cache.layout.groups) and not eng.cache.requests
+    compared = 0
+    for i, (prompt, got) in enumerate(zip(prompts, outs)):
+        assert len(got) == 30
+        if dtype == "float32":
+            want, margins = plain_greedy(raw, tensors, prompt, 30)
+            clear = next((j for j, m in enumerate(margins) if m < 1e-3), 30)
+            assert list(got[:clear]) == want[:clear], f"prompt of {len(prompt)} tokens"
+            compared += clear
+        else:
+            rid = f"alone{i}"
+            eng.runner.admit(rid)
+            whole = list(prompt) + list(got)
+            logits, _ = feed(eng.runner, rid, whole, [8] * (len(whole) // 8 + 1))           # (the engine's steps take 10 tokens)
+            logits = logits[len(prompt) - 1: len(whole) - 1]
+            eng.runner.release(rid)
+            for j, tok in enumerate(got):
+                assert logits[j, tok] >= logits[j].max() - 0.1, f"prompt {i}, new token {j}"
+            compared += 30
+    assert compared >= 40, "the margins left too little to compare"
+
+
+@pytest.mark.gpu
+def test_trace_replay_program(folders, tmp_path):
+    folder, raw, tensors = folders("full", FULL, seed=1)
+    a, b = tokens_for(raw, 60, 1), tokens_for(raw, 9, 2)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[30:31], "want": [0]}, {"id": "b", "tokens": b[:8], "want": [7]}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": a[31:58], "want": []}], "end": []},
+        {"step": 3, "entries": [{"id": "b", "tokens": b[8:], "want": [0]}, {"id": "a", "tokens": a[58:], "want": [0, 1]}], "end": ["a", "b"]},
+    ]
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32",
+                           "--out", str(out), "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [line for line in proc.stdout.splitlines() if line.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    assert not (out / "2.f32").exists()
+    wa, wb = plain.forward(raw, tensors, a), plain.forward(raw, tensors, b)
+    V = raw["vocab"]
+    got = {i: torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)) for i in (0, 1, 3)}
+    assert_close(got[0], wa[[0, 29]], "float32", "step 0")
+    assert_close(got[1], torch.stack([wa[30], wb[7]]), "float32", "step 1")
+    assert_close(got[3], torch.stack([wb[8], wa[58], wa[59]]), "float32", "step 3")
+
+
+@pytest.mark.gpu
+def test_command_line_with_random_weights(tmp_path):
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(FULL))
+    base = [sys.executable, "-m", "edgerag_b200", "--dtype", "fp32", "--num-blocks", "16", "--max-batch-size", "2", "--chunk-size", "16",
+            "--max-new-tokens", "5", "--prompt-ids", "3,1,4,1,5,9,2,6", "--prompt-ids", "7", "--json"]
+    first = subprocess.run(base + ["--random-weights", "3", "--config", str(cfg), "--save-model", str(tmp_path / "m"), "--weights-std", "0.1"],
+                           capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert first.returncode == 0, first.stderr[-2000:]
+    again = subprocess.run(base + ["--model", str(tmp_path / "m")], capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert again.returncode == 0, again.stderr[-2000:]
+    a, b = (json.loads(p.stdout.strip().splitlines()[-1])["outputs"] for p in (first, again))
+    assert [len(o["token_ids"]) for o in a] == [5, 5] and a == b
