@@ -3,8 +3,8 @@
 //
 //   1. route:   z = W_router x (float), s = sigmoid(z); the `top` experts with the largest z (the lower index wins a tie);
 //               per token the chosen experts and their scores s.  A (token, choice) is a "pair", numbered token * top + choice.
-//   2. lists:   count the pairs of every expert, make the offsets (and the offsets in row tiles), write the pair numbers of
-//               every expert in rising order behind its offset.
+//   2. lists:   one block per expert counts all choices, makes its offset (and its offset in row tiles) and writes the
+//               pair numbers of its expert in rising order behind the offset.
 //   3. gate/up: for every expert the rows of its pairs, each row the token's input times the pair's score (rounded to T
 //               once), times [W_gate; W_up]^T; act = silu(gate) * up, stored in the order of the lists.
 //   4. down:    act times W_down^T, stored as float at [choice][token][:]: the partial sums of the tokens' updates, which
@@ -19,21 +19,36 @@ ERB_DEFINE_LAST_ERROR(erb_last_error)
 
 namespace {
 
-constexpr int kRouteThreads = 128;
+constexpr int kRouteThreads = 256;
 
-// One block per token.  Shared memory: n_experts floats.
+// One block per token.  Shared memory: n_experts floats, then the token's row as floats.  A warp takes an expert at a
+// time; a lane sums the entries 4 lane .. 4 lane + 3 of every run of 128 (four runs in flight), then the lanes are added:
+// one order of sums whatever the batch.
 template <typename T>
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const T* __restrict__ x, int ld, const float* __restrict__ w_router, int width, int n_experts, int top,
                  int* __restrict__ choice, float* __restrict__ score) {
   chain_wait();
   extern __shared__ float z_s[];
+  float* x_s = z_s + ((n_experts + 3) & ~3);     // (16-byte aligned)
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const T* row = x + (size_t)t * ld;
+  for (int k = threadIdx.x; k < width; k += kRouteThreads) x_s[k] = Elem<T>::load(row + k);
+  __syncthreads();
+  const int whole = (width & 3) == 0 ? width & ~127 : 0;       // entries read as float4 by whole warps
   for (int e = warp; e < n_experts; e += kRouteThreads / 32) {
     const float* w = w_router + (size_t)e * width;
     float acc = 0.f;
-    for (int k = lane; k < width; k += 32) acc = fmaf(Elem<T>::load(row + k), w[k], acc);
+#pragma unroll 4
+    for (int k = 4 * lane; k < whole; k += 128) {
+      const float4 wv = *reinterpret_cast<const float4*>(w + k);
+      const float4 xv = *reinterpret_cast<const float4*>(x_s + k);
+      acc = fmaf(xv.x, wv.x, acc);
+      acc = fmaf(xv.y, wv.y, acc);
+      acc = fmaf(xv.z, wv.z, acc);
+      acc = fmaf(xv.w, wv.w, acc);
+    }
+    for (int k = whole + lane; k < width; k += 32) acc = fmaf(x_s[k], w[k], acc);
     acc = warp_sum(acc);
     if (lane == 0) z_s[e] = acc;
   }
@@ -61,41 +76,37 @@ moe_route_kernel(const T* __restrict__ x, int ld, const float* __restrict__ w_ro
   }
 }
 
-// One block per expert: how many pairs chose it.
-__global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ choice, int n_pairs, int* __restrict__ counts) {
+// One block per expert e builds the expert's part of the lists on its own: a histogram of all choices in shared memory
+// gives offsets[e] (the pairs of the experts before e) and tiles[e] (their row tiles of `tile_rows` rows); then the pairs
+// that chose e are written behind the offset in rising order.  The last block also writes the totals at [n_experts].
+__global__ void __launch_bounds__(256) moe_lists_kernel(const int* __restrict__ choice, int n_pairs, int n_experts, int tile_rows,
+                                                        int* __restrict__ counts, int* __restrict__ offsets,
+                                                        int* __restrict__ tiles, int* __restrict__ order) {
   chain_wait();
-  __shared__ float scratch[32];
-  const int e = blockIdx.x;
-  int c = 0;
-  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) c += choice[i] == e;
-  const float total = block_sum((float)c, scratch);      // (exact: counts stay far below 2^24)
-  if (threadIdx.x == 0) counts[e] = (int)total;
-}
-
-// One block: offsets[e] = pairs of the experts before e; tiles[e] = row tiles (of `tile_rows`) of the experts before e.
-__global__ void moe_offsets_kernel(const int* __restrict__ counts, int n_experts, int tile_rows, int* __restrict__ offsets,
-                                   int* __restrict__ tiles) {
-  chain_wait();
-  if (threadIdx.x != 0) return;
-  int off = 0, tl = 0;
-  for (int e = 0; e < n_experts; ++e) {
-    offsets[e] = off;
-    tiles[e] = tl;
-    off += counts[e];
-    tl += (counts[e] + tile_rows - 1) / tile_rows;
-  }
-  offsets[n_experts] = off;
-  tiles[n_experts] = tl;
-}
-
-// One block per expert: its pairs, in rising order, behind its offset.
-__global__ void __launch_bounds__(256) moe_fill_kernel(const int* __restrict__ choice, int n_pairs, const int* __restrict__ offsets,
-                                                       int* __restrict__ order) {
-  chain_wait();
+  extern __shared__ int hist[];                  // [n_experts]
   __shared__ int warp_counts[8];
   __shared__ int base_s;
   const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) base_s = offsets[e];
+  for (int i = threadIdx.x; i < n_experts; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&hist[choice[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0, tl = 0;
+    for (int i = 0; i < e; ++i) {
+      off += hist[i];
+      tl += (hist[i] + tile_rows - 1) / tile_rows;
+    }
+    counts[e] = hist[e];
+    offsets[e] = off;
+    tiles[e] = tl;
+    base_s = off;
+    if (e == n_experts - 1) {
+      offsets[n_experts] = off + hist[e];
+      tiles[n_experts] = tl + (hist[e] + tile_rows - 1) / tile_rows;
+      counts[n_experts] = 0;
+    }
+  }
   __syncthreads();
   for (int i0 = 0; i0 < n_pairs; i0 += 256) {
     const int i = i0 + threadIdx.x;
@@ -217,22 +228,25 @@ moe_product_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weigh
 ERB_EXPORT int erb_moe_tile_rows() { return kTM; }
 
 ERB_EXPORT int erb_moe_route(const void* x, int ld, const float* w_router, int n_tokens, int width, int n_experts, int top,
-                             int* choice, float* score, int* counts, int* offsets, int* tiles, int* order, void* stream) {
+                             int* choice, float* score, int* counts, int* offsets, int* tiles, int* order, int tile_rows,
+                             void* stream) {
   if (n_tokens <= 0) return ERB_OK;
   if (width <= 0 || n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 8192)
     return fail(ERB_ERR_ARG, "moe_route: %d of %d experts", top, n_experts);
   cudaStream_t s = (cudaStream_t)stream;
   const int n_pairs = n_tokens * top;
-  launch_chained(moe_route_kernel<elem_t>, dim3(n_tokens), dim3(kRouteThreads), sizeof(float) * n_experts, s, (const elem_t*)x, ld,
+  const size_t route_smem = sizeof(float) * ((size_t)((n_experts + 3) & ~3) + width);
+  if (route_smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(moe_route_kernel<elem_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem);
+    if (err != cudaSuccess) return fail(ERB_ERR_CUDA, "moe_route: %s", cudaGetErrorString(err));
+  }
+  launch_chained(moe_route_kernel<elem_t>, dim3(n_tokens), dim3(kRouteThreads), route_smem, s, (const elem_t*)x, ld,
                  w_router, width, n_experts, top, choice, score);
   int rc = check_launch("moe_route");
   if (rc) return rc;
-  launch_chained(moe_count_kernel, dim3(n_experts), dim3(256), 0, s, (const int*)choice, n_pairs, counts);
-  if ((rc = check_launch("moe_count"))) return rc;
-  launch_chained(moe_offsets_kernel, dim3(1), dim3(32), 0, s, (const int*)counts, n_experts, kTM, offsets, tiles);
-  if ((rc = check_launch("moe_offsets"))) return rc;
-  launch_chained(moe_fill_kernel, dim3(n_experts), dim3(256), 0, s, (const int*)choice, n_pairs, (const int*)offsets, order);
-  return check_launch("moe_fill");
+  launch_chained(moe_lists_kernel, dim3(n_experts), dim3(256), sizeof(int) * n_experts, s, (const int*)choice, n_pairs, n_experts,
+                 tile_rows > 0 ? tile_rows : kTM, counts, offsets, tiles, order);
+  return check_launch("moe_lists");
 }
 
 // gated != 0: act[list row][n_out] = silu(gate) * up from x (gathered, scaled); else parts[choice][token][n_out] from act rows.

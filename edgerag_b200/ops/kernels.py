@@ -104,7 +104,13 @@ _SIGNATURES = {
                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "erb_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                      c_void_p, c_void_p, c_void_p],
+                      c_void_p, c_void_p, c_int, c_void_p],
+    "erb_moe_tc_tile_rows": [c_longlong, c_int],
+    "erb_moe_tc_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "erb_moe_tc_gate_up": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                           c_void_p, c_void_p],
+    "erb_moe_tc_down": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                        c_void_p, c_void_p],
     "erb_moe_product": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                         c_int, c_int, c_void_p, c_void_p, c_void_p],
     "erb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -114,7 +120,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
-_LAUNCHES = {"erb_moe_route": 4, "erb_linear_batched": 0, "erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
+_LAUNCHES = {"erb_moe_route": 2, "erb_linear_batched": 0, "erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
 SKINNY_MAX_ROWS = 16     # rows up to which the register-fed weight-streaming kernels are used
 TC_MAX_ROWS = 64         # rows up to which the TMA + tcgen05 weight-streaming kernel may be used
 
@@ -1086,11 +1092,14 @@ def _moe_lists(lists: torch.Tensor, n_tokens: int, n_experts: int, top: int):
     return choice, order, counts, offsets, tiles
 
 
-def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, lists: torch.Tensor, score: torch.Tensor) -> None:
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, lists: torch.Tensor, score: torch.Tensor,
+              tile_rows: int = 0) -> None:
     """Route every row of ``x`` (element type, row-strided view allowed): logits ``w_router x`` in float (``w_router``
     float ``[experts, width]``), the ``top`` largest chosen (the lower index wins a tie), ``score`` float ``[tokens *
     top]`` their sigmoids; ``lists`` (int32, ``moe_lists_ints`` entries) receives the choices and, per expert, the list
-    of its (token, choice) pairs in rising order with offsets, all made on the device."""
+    of its (token, choice) pairs in rising order with offsets, all made on the device.  ``tile_rows``: the rows of a tile
+    that the lists' tile offsets count (0: those of ``moe_gate_up`` and ``moe_down``; ``moe_tc_tile_rows`` for the
+    tensor-core products)."""
     _need(x, "x", contiguous=False); _need(w_router, "w_router", torch.float32); _need(lists, "lists", torch.int32)
     _need(score, "score", torch.float32)
     n, width = x.shape
@@ -1100,7 +1109,57 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, lists: torch.Te
     choice, order, counts, offsets, tiles = _moe_lists(lists, n, n_experts, top)
     _call(_fn("moe", _elem(x), "erb_moe_route"), x.data_ptr(), x.stride(0) if n > 1 else width, w_router.data_ptr(), n, width,
           n_experts, int(top), choice.data_ptr(), score.data_ptr(), counts.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
-          order.data_ptr(), _stream())
+          order.data_ptr(), int(tile_rows), _stream())
+
+
+def moe_tc_supported(dtype: torch.dtype, width: int, ff: int) -> bool:
+    """Shapes the tensor-core products of the routed experts take: bfloat16, rows of whole 16-byte pieces."""
+    return dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0
+
+
+def moe_tc_tile_rows(n_tokens: int, n_experts: int, top: int) -> int:
+    """Rows of a tile of the tensor-core products for this many tokens: 16 to 128, the smallest that holds an expert's
+    even share of the (token, choice) pairs."""
+    fn = native.load("moe_tc", None).erb_moe_tc_tile_rows
+    fn.argtypes, fn.restype = _SIGNATURES["erb_moe_tc_tile_rows"], c_int
+    return int(fn(n_tokens * top, n_experts))
+
+
+def moe_tc_gather(x: torch.Tensor, lists: torch.Tensor, score: torch.Tensor, n_experts: int, top: int, xs: torch.Tensor) -> None:
+    """xs[list row] = round(score * x[token]) for every (token, choice) pair, in the order of the experts' lists."""
+    _need(x, "x", torch.bfloat16, contiguous=False); _need(xs, "xs", torch.bfloat16); _need(score, "score", torch.float32)
+    n, width = x.shape
+    if xs.shape != (n * top, width) or x.stride(1) != 1:
+        raise KernelError("moe_tc_gather: shapes disagree")
+    _, order, _, _, _ = _moe_lists(lists, n, n_experts, top)
+    _call(_fn("moe_tc", None, "erb_moe_tc_gather"), x.data_ptr(), x.stride(0) if n > 1 else width, order.data_ptr(), score.data_ptr(),
+          int(top), n, width, xs.data_ptr(), _stream())
+
+
+def moe_tc_gate_up(xs: torch.Tensor, w_gate_up: torch.Tensor, lists: torch.Tensor, top: int, tile_rows: int, act: torch.Tensor) -> None:
+    """``moe_gate_up`` on tensor cores, from the gathered and scaled rows ``xs`` of ``moe_tc_gather``; the lists must have
+    been made with ``tile_rows`` rows a tile."""
+    _need(xs, "xs", torch.bfloat16); _need(w_gate_up, "w_gate_up", torch.bfloat16); _need(act, "act", torch.bfloat16)
+    pairs, width = xs.shape
+    n_experts, two_ff, k = w_gate_up.shape
+    if k != width or two_ff % 2 or pairs % top or act.shape != (pairs, two_ff // 2):
+        raise KernelError("moe_tc_gate_up: shapes disagree")
+    _, order, _, offsets, tiles = _moe_lists(lists, pairs // top, n_experts, top)
+    _call(_fn("moe_tc", None, "erb_moe_tc_gate_up"), xs.data_ptr(), w_gate_up.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
+          order.data_ptr(), n_experts, int(top), pairs // top, two_ff // 2, width, int(tile_rows), act.data_ptr(), _ptr(_status_word),
+          _stream())
+
+
+def moe_tc_down(act: torch.Tensor, w_down: torch.Tensor, lists: torch.Tensor, top: int, tile_rows: int, parts: torch.Tensor) -> None:
+    """``moe_down`` on tensor cores; the lists must have been made with ``tile_rows`` rows a tile."""
+    _need(act, "act", torch.bfloat16); _need(w_down, "w_down", torch.bfloat16); _need(parts, "parts", torch.float32)
+    n_experts, width, ff = w_down.shape
+    n = act.shape[0] // top
+    if act.shape != (n * top, ff) or parts.dim() != 3 or parts.shape[0] < top or parts.shape[1:] != (n, width):
+        raise KernelError("moe_tc_down: shapes disagree")
+    _, order, _, offsets, tiles = _moe_lists(lists, n, n_experts, top)
+    _call(_fn("moe_tc", None, "erb_moe_tc_down"), act.data_ptr(), w_down.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
+          order.data_ptr(), n_experts, int(top), n, width, ff, int(tile_rows), parts.data_ptr(), _ptr(_status_word), _stream())
 
 
 def moe_gate_up(x: torch.Tensor, w_gate_up: torch.Tensor, lists: torch.Tensor, score: torch.Tensor, top: int,

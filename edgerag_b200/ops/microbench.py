@@ -454,11 +454,21 @@ def routed_experts(a) -> dict:
         state["i"] = (state["i"] + 1) % reps
         return state["i"]
 
-    kernels.moe_route(x, router, top, lists, score)
+    tc = kernels.moe_tc_supported(dtype, h, ff) and not getattr(a, "general", False)     # as the feed-forward part chooses
+    tile_rows = kernels.moe_tc_tile_rows(n, E, top) if tc else 0
+    kernels.moe_route(x, router, top, lists, score, tile_rows)
     used = int((lists[2 * n * top: 2 * n * top + E] > 0).sum())     # experts that some row chose
-    us_route = _time(lambda: kernels.moe_route(x, router, top, lists, score), a.iters, a.warmup)
-    us_up = _time(lambda: kernels.moe_gate_up(x, wgu[rotate()], lists, score, top, act), max(a.iters, 2 * reps), a.warmup)
-    us_down = _time(lambda: kernels.moe_down(act, wd[rotate()], lists, top, parts), max(a.iters, 2 * reps), a.warmup)
+    us_route = _time(lambda: kernels.moe_route(x, router, top, lists, score, tile_rows), a.iters, a.warmup)
+    us_gather = 0.0
+    if tc:
+        xs = torch.empty((n * top, h), dtype=dtype, device="cuda")
+        kernels.moe_tc_gather(x, lists, score, E, top, xs)
+        us_gather = _time(lambda: kernels.moe_tc_gather(x, lists, score, E, top, xs), a.iters, a.warmup)
+        us_up = _time(lambda: kernels.moe_tc_gate_up(xs, wgu[rotate()], lists, top, tile_rows, act), max(a.iters, 2 * reps), a.warmup)
+        us_down = _time(lambda: kernels.moe_tc_down(act, wd[rotate()], lists, top, tile_rows, parts), max(a.iters, 2 * reps), a.warmup)
+    else:
+        us_up = _time(lambda: kernels.moe_gate_up(x, wgu[rotate()], lists, score, top, act), max(a.iters, 2 * reps), a.warmup)
+        us_down = _time(lambda: kernels.moe_down(act, wd[rotate()], lists, top, parts), max(a.iters, 2 * reps), a.warmup)
     # the dense feed-forward of the same arithmetic per token
     dgu = [(torch.randn((2 * top * ff, h), device="cuda") * 0.02).to(dtype) for _ in range(max(1, reps // 4))]
     dd = [(torch.randn((h, top * ff), device="cuda") * 0.02).to(dtype) for _ in range(max(1, reps // 4))]
@@ -476,7 +486,7 @@ def routed_experts(a) -> dict:
 
     dense_bytes_up, dense_bytes_down = 2 * top * ff * h * item + n * h * item, top * ff * h * item + n * top * ff * item
     return {"case": "routed-experts", "tokens": n, "experts": E, "top": top, "ff": ff, "width": h, "experts_used": used,
-            "route_us": round(us_route, 2), "gate_up": line(us_up, flops_up, bytes_up), "down": line(us_down, flops_down, bytes_down),
+            "tensor_cores": bool(tc), "tile_rows": tile_rows, "route_us": round(us_route, 2), "gather_us": round(us_gather, 2), "gate_up": line(us_up, flops_up, bytes_up), "down": line(us_down, flops_down, bytes_down),
             "dense_gate_up": line(us_dense_up, flops_up, dense_bytes_up), "dense_down": line(us_dense_down, flops_down, dense_bytes_down)}
 
 
@@ -565,6 +575,7 @@ def main(argv=None) -> int:
     re.add_argument("--ff", type=int, default=1024)
     re.add_argument("--experts", type=int, default=32)
     re.add_argument("--top", type=int, default=4)
+    re.add_argument("--general", action="store_true", help="the products on CUDA cores (what float32 runs) instead of tensor cores")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)

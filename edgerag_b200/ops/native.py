@@ -35,6 +35,7 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...], bool]] = {
     "ssm": ("ssm.cu", (), True),
     "delta": ("delta.cu", (), True),
     "moe": ("moe.cu", (), True),
+    "moe_tc": ("moe_tc.cu", ("-lcuda",), False),
     "attention_tc": ("attention_tc.cu", ("-lcuda",), False),
     "attention_prefill": ("attention_prefill.cu", ("-lcuda",), False),
     "gemm": ("gemm.cu", ("-lcublasLt",), True),

@@ -68,11 +68,20 @@ class RoutedExperts(FeedForward):
         n, top = x.shape[0], self.top
         lists = ctx.buf("moe.lists", (kernels.moe_lists_ints(n, self.n_experts, top),), torch.int32)
         score = ctx.buf("moe.score", (n * top,), torch.float32)
-        kernels.moe_route(x, self.w_router, top, lists, score)
         act = ctx.buf("moe.act", (n * top, self.intermediate), self.dtype)
-        kernels.moe_gate_up(x, self.w_gate_up, lists, score, top, act)
         parts = ctx.buf("ffn.out_parts", (top + (self.shared is not None), n, self.hidden), torch.float32)
-        kernels.moe_down(act, self.w_down, lists, top, parts)
+        if kernels.moe_tc_supported(self.dtype, self.hidden, self.intermediate):
+            # tensor cores: row tiles sized by the step's tokens, the scaled rows gathered once in list order
+            tile_rows = kernels.moe_tc_tile_rows(n, self.n_experts, top)
+            kernels.moe_route(x, self.w_router, top, lists, score, tile_rows)
+            xs = ctx.buf("moe.rows", (n * top, self.hidden), self.dtype)
+            kernels.moe_tc_gather(x, lists, score, self.n_experts, top, xs)
+            kernels.moe_tc_gate_up(xs, self.w_gate_up, lists, top, tile_rows, act)
+            kernels.moe_tc_down(act, self.w_down, lists, top, tile_rows, parts)
+        else:
+            kernels.moe_route(x, self.w_router, top, lists, score)
+            kernels.moe_gate_up(x, self.w_gate_up, lists, score, top, act)
+            kernels.moe_down(act, self.w_down, lists, top, parts)
         if self.shared is not None:
             self.shared.forward_into(x, ctx, parts[top])
         return parts

@@ -156,18 +156,25 @@ def row_errors(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
     return d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-9)
 
 
-#: (worst row, mean over rows).  float32: only the order of sums differs from the plain implementation.  bfloat16:
-#: activations are rounded to 8 bits between the products, and every sublayer's output is brought to unit RMS, which
-#: carries a small output's rounding into the stream at full size: single rows of a model of 7 narrow layers reach 11 %.
-#: The float32 runs are the sharp ones; the models made to show a fault move rows by 50 % and more.
-BANDS = {"float32": (3e-4, 6e-5), "bfloat16": (2e-1, 3.5e-2)}
+#: float32 (worst row, mean over rows): only the order of sums differs from the plain implementation.
+#: bfloat16 (mean over rows, the level that 2 % of the rows may pass, the level that none may): activations are rounded
+#: to 8 bits between the products, and every sublayer's output is brought to unit RMS, which carries the rounding of a
+#: small output into the stream at full size.  Where a head's read-out of 8 entries is close to zero, single rows of
+#: the narrow 7-layer model reach 10 to 20 % (the float32 runs have their worst rows at the same places, 5 times their
+#: mean).  The float32 runs are the sharp ones; the models made to show a fault move rows by 50 % and more.
+BANDS = {"float32": (3e-4, 6e-5), "bfloat16": (3.5e-2, 0.1, 0.5)}
 
 
 def assert_close(got, want, dtype, what=""):
     assert torch.isfinite(got).all(), f"{what} {dtype}: non-finite logits"
     e = row_errors(got, want)
-    worst, mean = BANDS[dtype]
-    assert e.max() <= worst and e.mean() <= mean, f"{what} {dtype}: worst {e.max():.2e} (row {int(e.argmax())}), mean {e.mean():.2e}"
+    where = f"{what} {dtype}: worst {e.max():.2e} (row {int(e.argmax())}), mean {e.mean():.2e}"
+    if dtype == "float32":
+        worst, mean = BANDS[dtype]
+        assert e.max() <= worst and e.mean() <= mean, where
+    else:
+        mean, few, none = BANDS[dtype]
+        assert e.mean() <= mean and e.max() <= none and int((e > few).sum()) <= max(1, len(e) // 50), where
 
 
 def tokens_for(raw, n, seed):
@@ -775,7 +782,7 @@ def test_head_norm_and_gate(dtype):
 
 MOE_CASES = [  # (tokens, width, ff, experts, top)
     (1, 64, 48, 4, 2), (7, 80, 24, 3, 3), (50, 72, 40, 5, 1), (130, 64, 136, 8, 2), (33, 128, 200, 16, 4), (3, 40, 8, 2, 1),
-    (300, 256, 192, 6, 2),
+    (300, 256, 192, 6, 2), (100, 64, 64, 4, 1), (700, 128, 264, 3, 2),
 ]
 
 
@@ -838,6 +845,28 @@ def test_routed_experts_kernels(case, dtype):
     err = (got - want).abs().max() / want.abs().max()
     assert err < (2e-5 if dtype == "float32" else 2e-2), f"{err:.2e}"
     assert torch.isnan(parts[top]).all(), "the shared expert's part was written"
+    if not k.moe_tc_supported(tdt, width, ff):
+        return
+    # the same on tensor cores, with row tiles of every size (the engine takes the smallest that holds an expert's share)
+    assert k.moe_tc_tile_rows(n, E, top) in (16, 32, 64, 128)
+    for tile_rows in (16, 32, 64, 128):
+        lists2 = torch.full_like(lists, -7)
+        k.moe_route(xd, t["router"].cuda(), top, lists2, score, tile_rows)
+        assert torch.equal(lists2[: 2 * pairs + 2 * (E + 1)], lists[: 2 * pairs + 2 * (E + 1)])
+        tiles = lists2[2 * pairs + 2 * (E + 1):].cpu().tolist()
+        assert tiles == [0] + list(np.cumsum([-(-c // tile_rows) for c in counts[:E].tolist()]))
+        xs = torch.full((pairs, width), float("nan"), dtype=tdt, device="cuda")
+        k.moe_tc_gather(xd, lists2, score, E, top, xs)
+        rows = (sc.view(-1)[order][:, None] * x.float()[order // top]).to(tdt)
+        assert torch.equal(xs.cpu(), rows)
+        act2 = torch.full((pairs, ff), float("nan"), dtype=tdt, device="cuda")
+        k.moe_tc_gate_up(xs, w_gate_up, lists2, top, tile_rows, act2)
+        assert (act2.float() - act.float()).abs().max() <= 0.02 * act.float().abs().max()
+        parts2 = torch.full((top + 1, n, width), float("nan"), device="cuda")
+        k.moe_tc_down(act2, w_down, lists2, top, tile_rows, parts2)
+        err = (parts2[:top].sum(0).cpu().double() - want).abs().max() / want.abs().max()
+        assert err < 2e-2, f"tensor cores, tiles of {tile_rows} rows: {err:.2e}"
+        assert torch.isnan(parts2[top]).all()
 
 
 @pytest.mark.gpu
@@ -868,6 +897,27 @@ def test_an_expert_does_not_depend_on_the_other_rows(dtype):
     big = run(x)
     assert torch.equal(run(x[17:18])[:, 0], big[:, 17])
     assert torch.equal(run(x[15:20])[:, 2], big[:, 17])
+    if not k.moe_tc_supported(tdt, width, ff):
+        return
+
+    def run_tc(rows):
+        n = rows.shape[0]
+        tile_rows = k.moe_tc_tile_rows(n, E, top)
+        lists = torch.empty(k.moe_lists_ints(n, E, top), dtype=torch.int32, device="cuda")
+        score = torch.empty(n * top, device="cuda")
+        k.moe_route(rows, router, top, lists, score, tile_rows)
+        xs = torch.empty(n * top, width, dtype=tdt, device="cuda")
+        k.moe_tc_gather(rows, lists, score, E, top, xs)
+        act = torch.empty(n * top, ff, dtype=tdt, device="cuda")
+        k.moe_tc_gate_up(xs, wgu, lists, top, tile_rows, act)
+        parts = torch.empty(top, n, width, device="cuda")
+        k.moe_tc_down(act, wd, lists, top, tile_rows, parts)
+        return parts.cpu(), tile_rows
+
+    big_tc, rows_big = run_tc(x)
+    one, rows_one = run_tc(x[17:18])
+    assert rows_big != rows_one, "the test's sizes give one tile size"
+    assert torch.equal(one[:, 0], big_tc[:, 17]) and torch.equal(run_tc(x[15:20])[0][:, 2], big_tc[:, 17])
 
 
 @pytest.mark.gpu
