@@ -101,7 +101,7 @@ _SIGNATURES = {
                            c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_void_p],
     "erb_delta_scan": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "erb_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_int, c_void_p],
@@ -120,7 +120,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
-_LAUNCHES = {"erb_moe_route": 2, "erb_linear_batched": 0, "erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
+_LAUNCHES = {"erb_moe_route": 2, "erb_delta_scan": 2, "erb_linear_batched": 0, "erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
 SKINNY_MAX_ROWS = 16     # rows up to which the register-fed weight-streaming kernels are used
 TC_MAX_ROWS = 64         # rows up to which the TMA + tcgen05 weight-streaming kernel may be used
 
@@ -1032,15 +1032,24 @@ def gated_group_norm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, e
 DELTA_MAX_KEY_DIM = 512      # entries of a key the scan kernel holds per column (32 lanes of 16)
 
 
+def delta_scratch_floats(n_tokens: int, n_heads: int, n_key_heads: int, key_dim: int, v_dim: int) -> int:
+    """Floats of the scratch ``delta_scan`` fills for a step of ``n_tokens`` tokens: per token the unit queries and keys of
+    every key head, three scalars per head and the values, rows padded to 16 bytes."""
+    pad = lambda v: (v + 3) & ~3   # noqa: E731
+    return n_tokens * (n_key_heads * 2 * pad(key_dim) + n_heads * 4 + n_heads * pad(v_dim))
+
+
 def delta_scan(qkv: torch.Tensor, proj: torch.Tensor, off_b: int, off_a: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
                state: torch.Tensor, n_seqs: int, seq_starts: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor,
-               n_key_heads: int, key_dim: int) -> None:
+               n_key_heads: int, key_dim: int, scratch: torch.Tensor | None = None) -> None:
     """The gated delta rule over every request's rows, from and to its record in ``state`` (float ``[slots, heads,
     vdim, key_dim]``, the matrix of a head stored with the value index first).  ``qkv``: convolved and activated rows
     ``[q (key heads * key_dim) | k (the same) | v (heads * vdim)]``; the raw write strengths and decay inputs are
     columns ``off_b .. off_b + heads`` and ``off_a .. off_a + heads`` of ``proj``.  Per token and head: q and k are
     made unit vectors (q also times ``key_dim ** -0.5``), ``beta = sigmoid(b)``, ``g = exp(-exp(a_log) * softplus(a +
-    dt_bias))``, ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``.  ``out`` float ``[tokens, heads * vdim]``."""
+    dt_bias))``, ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``.  ``out`` float ``[tokens, heads * vdim]``.
+    ``scratch``: float, ``delta_scratch_floats`` entries (None: allocated here), where a first kernel leaves every token's
+    unit vectors, scalars and values for the walk along the tokens."""
     _need(qkv, "qkv"); _need(proj, "proj", qkv.dtype, contiguous=False); _need(state, "state", torch.float32)
     _need(out, "out", torch.float32); _need(dt_bias, "dt_bias", torch.float32); _need(a_log, "a_log", torch.float32)
     _need(seq_starts, "seq_starts", torch.int32); _need(state_slots, "state_slots", torch.int32)
@@ -1050,9 +1059,15 @@ def delta_scan(qkv: torch.Tensor, proj: torch.Tensor, off_b: int, off_a: int, dt
             proj.shape[0] != n or max(off_b, off_a) + heads > proj.shape[1] or dt_bias.numel() != heads or \
             a_log.numel() != heads or heads % n_key_heads or seq_starts.numel() < n_seqs + 1 or state_slots.numel() < n_seqs:
         raise KernelError("delta_scan: shapes disagree")
+    need = delta_scratch_floats(n, heads, n_key_heads, d, vdim)
+    if scratch is None:
+        scratch = torch.empty(max(need, 4), dtype=torch.float32, device=qkv.device)
+    _need(scratch, "scratch", torch.float32)
+    if scratch.numel() < need:
+        raise KernelError("delta_scan: the scratch is too small")
     _call(_fn("delta", _elem(qkv), "erb_delta_scan"), qkv.data_ptr(), qkv.shape[1], proj.data_ptr(),
           proj.stride(0) if n > 1 else proj.shape[1], int(off_b), int(off_a), dt_bias.data_ptr(), a_log.data_ptr(),
-          state.data_ptr(), seq_starts.data_ptr(), state_slots.data_ptr(), out.data_ptr(), int(n_seqs), n, heads,
+          state.data_ptr(), seq_starts.data_ptr(), state_slots.data_ptr(), out.data_ptr(), scratch.data_ptr(), int(n_seqs), n, heads,
           int(n_key_heads), d, vdim, _stream())
 
 

@@ -421,7 +421,9 @@ def delta_scan(a) -> dict:
     y = torch.empty((n, inner), device="cuda")
     starts = (torch.arange(a.batch + 1, dtype=torch.int32) * a.tokens).cuda()
     slots = torch.arange(a.batch, dtype=torch.int32).cuda()
-    fn = lambda: kernels.delta_scan(qkv, proj, 0, a.heads, vec[0], vec[1], state, a.batch, starts, slots, y, a.key_heads, a.key_dim)  # noqa: E731
+    scratch = torch.empty(kernels.delta_scratch_floats(n, a.heads, a.key_heads, a.key_dim, a.head_dim), device="cuda")
+    fn = lambda: kernels.delta_scan(qkv, proj, 0, a.heads, vec[0], vec[1], state, a.batch, starts, slots, y, a.key_heads, a.key_dim,  # noqa: E731
+                                    scratch)
     us = _time(fn, a.iters, a.warmup)
     item = 2 if dtype == torch.bfloat16 else 4
     nbytes = 2 * state.numel() * 4 + n * (ch * item + inner * 4)

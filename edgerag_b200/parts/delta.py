@@ -90,7 +90,9 @@ class GatedDeltaRule(Mixer):
                               ctx.seq_of_token, ctx.seq_starts, ctx.state_slots, qkv)
         o = ctx.buf("delta.o", (n, self.inner), torch.float32)
         kernels.delta_scan(qkv, proj, self.off_b, self.off_a, self.dt_bias, self.a_log, ctx.state("delta", call.cache_layer),
-                           ctx.n_seqs, ctx.seq_starts, ctx.state_slots, o, self.n_key_heads, self.key_dim)
+                           ctx.n_seqs, ctx.seq_starts, ctx.state_slots, o, self.n_key_heads, self.key_dim,
+                           ctx.buf("delta.scratch", (kernels.delta_scratch_floats(n, self.n_heads, self.n_key_heads, self.key_dim,
+                                                                                  self.v_dim),), torch.float32))
         gated = ctx.buf("delta.gated", (n, self.inner), self.dtype)
         kernels.head_norm_gate(o, proj[:, self.off_gate: self.off_gate + self.inner], self.norm_w, gated, self.n_heads, self.eps)
         n_parts = kernels.linear_parts_count(gated, self.w_o)

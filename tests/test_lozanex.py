@@ -161,7 +161,9 @@ def row_errors(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
 #: to 8 bits between the products, and every sublayer's output is brought to unit RMS, which carries the rounding of a
 #: small output into the stream at full size.  Where a head's read-out of 8 entries is close to zero, single rows of
 #: the narrow 7-layer model reach 10 to 20 % (the float32 runs have their worst rows at the same places, 5 times their
-#: mean).  The float32 runs are the sharp ones; the models made to show a fault move rows by 50 % and more.
+#: mean).  The first rows of a sequence are the worst conditioned: weights moved by 2^-9 in the plain float64
+#: implementation move the logits of rows 0 and 1 of that model by 40 %, those of later rows by 4 % on average.
+#: The float32 runs are the sharp ones; the models made to show a fault move rows by 50 % and more.
 BANDS = {"float32": (3e-4, 6e-5), "bfloat16": (3.5e-2, 0.1, 0.5)}
 
 
@@ -174,7 +176,7 @@ def assert_close(got, want, dtype, what=""):
         assert e.max() <= worst and e.mean() <= mean, where
     else:
         mean, few, none = BANDS[dtype]
-        assert e.mean() <= mean and e.max() <= none and int((e > few).sum()) <= max(1, len(e) // 50), where
+        assert e.mean() <= mean and e.max() <= none and int((e > few).sum()) <= max(3, len(e) // 50), where
 
 
 def tokens_for(raw, n, seed):
