@@ -1393,6 +1393,93 @@ rms_between_kernel(float* __restrict__ hidden, const T* __restrict__ delta, cons
   for (int i = threadIdx.x; i < width; i += blockDim.x) Elem<T>::store(y + i, row[i] * rs * w[i]);
 }
 
+// The same for rows of whole 16-byte pieces without a norm of the stream itself: the row and the update stay in registers
+// (V pieces a thread), every load is on its way before the first sum.
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+rms_between_vec_kernel(float* __restrict__ hidden, const T* __restrict__ delta, const float* __restrict__ parts, int n_parts,
+                       size_t part_stride, const float* __restrict__ bias, const float* __restrict__ post_w, float post_eps,
+                       const float* __restrict__ w, float eps, T* __restrict__ out, int out_ld, const int* __restrict__ rows,
+                       int width, int write_back) {
+  chain_wait();
+  __shared__ float scratch[32];
+  const int o = blockIdx.x;
+  const int r = rows ? rows[o] : o;
+  float* h = hidden + (size_t)r * width;
+  const int n4 = width / 4;
+  const float inv_w = 1.f / (float)width;
+  float4 row[V], upd[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    const int i = threadIdx.x + v * 256;
+    row[v] = i < n4 ? reinterpret_cast<const float4*>(h)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const bool has_update = delta || parts;
+  if (has_update) {
+    float dsq = 0.f;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      const int i = threadIdx.x + v * 256;
+      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < n4) {
+        if (delta) {
+          const T* d = delta + (size_t)r * width + 4 * i;
+          u = make_float4(Elem<T>::load(d), Elem<T>::load(d + 1), Elem<T>::load(d + 2), Elem<T>::load(d + 3));
+        } else {
+          const float* ps = parts + (size_t)r * width + 4 * i;
+          u = *reinterpret_cast<const float4*>(ps);
+          for (int sp = 1; sp < n_parts; ++sp) {
+            const float4 q = *reinterpret_cast<const float4*>(ps + sp * part_stride);
+            u.x += q.x; u.y += q.y; u.z += q.z; u.w += q.w;
+          }
+          u = make_float4(Elem<T>::round(u.x), Elem<T>::round(u.y), Elem<T>::round(u.z), Elem<T>::round(u.w));
+        }
+        if (bias) {
+          const float4 b = reinterpret_cast<const float4*>(bias)[i];
+          u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+        }
+      }
+      upd[v] = u;
+      dsq += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+    }
+    float rs = 1.f;
+    if (post_w) rs = rsqrtf(block_sum(dsq, scratch) * inv_w + post_eps);
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      const int i = threadIdx.x + v * 256;
+      if (i >= n4) continue;
+      float4 pw = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (post_w) pw = reinterpret_cast<const float4*>(post_w)[i];
+      row[v].x += post_w ? upd[v].x * rs * pw.x : upd[v].x;
+      row[v].y += post_w ? upd[v].y * rs * pw.y : upd[v].y;
+      row[v].z += post_w ? upd[v].z * rs * pw.z : upd[v].z;
+      row[v].w += post_w ? upd[v].w * rs * pw.w : upd[v].w;
+      if (write_back) reinterpret_cast<float4*>(h)[i] = row[v];
+    }
+  }
+  if (!out) return;
+  T* y = out + (size_t)o * out_ld;
+  float rs = 1.f;
+  if (w) {
+    float s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < V; ++v) s2 += row[v].x * row[v].x + row[v].y * row[v].y + row[v].z * row[v].z + row[v].w * row[v].w;
+    rs = rsqrtf(block_sum(s2, scratch) * inv_w + eps);
+  }
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    const int i = threadIdx.x + v * 256;
+    if (i >= n4) continue;
+    float4 ww = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (w) ww = reinterpret_cast<const float4*>(w)[i];
+    T* dst = y + 4 * i;
+    Elem<T>::store(dst, w ? row[v].x * rs * ww.x : row[v].x);
+    Elem<T>::store(dst + 1, w ? row[v].y * rs * ww.y : row[v].y);
+    Elem<T>::store(dst + 2, w ? row[v].z * rs * ww.z : row[v].z);
+    Elem<T>::store(dst + 3, w ? row[v].w * rs * ww.w : row[v].w);
+  }
+}
+
 ERB_EXPORT int erb_rms_between(void* hidden, const void* delta, int n_parts, long long part_stride, const float* bias,
                                const float* self_w, float self_eps, const float* post_w, float post_eps, const float* w,
                                float eps, void* out, int out_ld, const int* rows, int n_rows, int width, int write_back,
@@ -1407,6 +1494,21 @@ ERB_EXPORT int erb_rms_between(void* hidden, const void* delta, int n_parts, lon
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "rms_between: %s", cudaGetErrorString(e));
   }
   const bool in_parts = n_parts > 0;
+  const bool aligned = !(((uintptr_t)hidden | (uintptr_t)delta | (uintptr_t)bias | (uintptr_t)post_w | (uintptr_t)w) & 15) &&
+                       (!in_parts || part_stride % 4 == 0);
+  if (!self_w && width % 4 == 0 && width <= 8192 && aligned) {
+    const int pieces = (width / 4 + 255) / 256;
+#define ERB_RMS_CASE(V)                                                                                                  \
+  launch_chained(rms_between_vec_kernel<elem_t, V>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, (float*)hidden,     \
+                 in_parts ? nullptr : (const elem_t*)delta, in_parts ? (const float*)delta : nullptr, n_parts,          \
+                 (size_t)part_stride, bias, post_w, post_eps, w, eps, (elem_t*)out, out_ld, rows, width, write_back)
+    if (pieces <= 1) ERB_RMS_CASE(1);
+    else if (pieces <= 2) ERB_RMS_CASE(2);
+    else if (pieces <= 4) ERB_RMS_CASE(4);
+    else ERB_RMS_CASE(8);
+#undef ERB_RMS_CASE
+    return check_launch("rms_between");
+  }
   launch_chained(kern, dim3(n_rows), dim3(width >= 1024 ? 256 : 128), smem, (cudaStream_t)stream, (float*)hidden,
                  in_parts ? nullptr : (const elem_t*)delta, in_parts ? (const float*)delta : nullptr, n_parts,
                  (size_t)part_stride, bias, self_w, self_eps, post_w, post_eps, w, eps, (elem_t*)out, out_ld, rows, width,

@@ -19,47 +19,68 @@ ERB_DEFINE_LAST_ERROR(erb_last_error)
 
 namespace {
 
-constexpr int kRouteThreads = 256;
+constexpr int kRouteThreads = 512;
 
-// One block per token.  Shared memory: n_experts floats, then the token's row as floats.  A warp takes an expert at a
-// time; a lane sums the entries 4 lane .. 4 lane + 3 of every run of 128 (four runs in flight), then the lanes are added:
-// one order of sums whatever the batch.
+// One block per kRouteTokens tokens.  Shared memory: their logits, then their rows as floats.  A warp takes an expert at
+// a time and reads its router row once for all the block's tokens; a lane sums the entries 4 lane .. 4 lane + 3 of every
+// run of 128, then the lanes are added: one order of sums per token whatever the batch.  Then a warp per token picks.
+constexpr int kRouteTokens = 4;
 template <typename T>
 __global__ void __launch_bounds__(kRouteThreads)
-moe_route_kernel(const T* __restrict__ x, int ld, const float* __restrict__ w_router, int width, int n_experts, int top,
-                 int* __restrict__ choice, float* __restrict__ score) {
+moe_route_kernel(const T* __restrict__ x, int ld, const float* __restrict__ w_router, int n_tokens, int width, int n_experts,
+                 int top, int* __restrict__ choice, float* __restrict__ score) {
   chain_wait();
-  extern __shared__ float z_s[];
-  float* x_s = z_s + ((n_experts + 3) & ~3);     // (16-byte aligned)
-  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const T* row = x + (size_t)t * ld;
-  for (int k = threadIdx.x; k < width; k += kRouteThreads) x_s[k] = Elem<T>::load(row + k);
+  extern __shared__ float z_s[];                 // [kRouteTokens][n_experts padded to 4], then [kRouteTokens][width]
+  const int e_pad = (n_experts + 3) & ~3;
+  float* x_s = z_s + kRouteTokens * e_pad;
+  const int t0 = blockIdx.x * kRouteTokens, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_here = min(kRouteTokens, n_tokens - t0);
+#pragma unroll
+  for (int j = 0; j < kRouteTokens; ++j) {
+    const T* row = x + (size_t)(t0 + min(j, n_here - 1)) * ld;
+#pragma unroll 4
+    for (int k = threadIdx.x; k < width; k += kRouteThreads) x_s[j * width + k] = Elem<T>::load(row + k);
+  }
   __syncthreads();
   const int whole = (width & 3) == 0 ? width & ~127 : 0;       // entries read as float4 by whole warps
   for (int e = warp; e < n_experts; e += kRouteThreads / 32) {
     const float* w = w_router + (size_t)e * width;
-    float acc = 0.f;
-#pragma unroll 4
-    for (int k = 4 * lane; k < whole; k += 128) {
+    float acc[kRouteTokens];
+#pragma unroll
+    for (int j = 0; j < kRouteTokens; ++j) acc[j] = 0.f;
+#pragma unroll 8
+    for (int k = 4 * lane; k < whole; k += 128) {            // (eight 16-byte reads of the router's row in flight a lane)
       const float4 wv = *reinterpret_cast<const float4*>(w + k);
-      const float4 xv = *reinterpret_cast<const float4*>(x_s + k);
-      acc = fmaf(xv.x, wv.x, acc);
-      acc = fmaf(xv.y, wv.y, acc);
-      acc = fmaf(xv.z, wv.z, acc);
-      acc = fmaf(xv.w, wv.w, acc);
+#pragma unroll
+      for (int j = 0; j < kRouteTokens; ++j) {
+        const float4 xv = *reinterpret_cast<const float4*>(x_s + j * width + k);
+        acc[j] = fmaf(xv.x, wv.x, acc[j]);
+        acc[j] = fmaf(xv.y, wv.y, acc[j]);
+        acc[j] = fmaf(xv.z, wv.z, acc[j]);
+        acc[j] = fmaf(xv.w, wv.w, acc[j]);
+      }
     }
-    for (int k = whole + lane; k < width; k += 32) acc = fmaf(x_s[k], w[k], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) z_s[e] = acc;
+    for (int k = whole + lane; k < width; k += 32) {
+      const float wv = w[k];
+#pragma unroll
+      for (int j = 0; j < kRouteTokens; ++j) acc[j] = fmaf(x_s[j * width + k], wv, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kRouteTokens; ++j) {
+      const float total = warp_sum(acc[j]);
+      if (lane == 0) z_s[j * e_pad + e] = total;
+    }
   }
   __syncthreads();
-  if (warp != 0) return;
+  if (warp >= n_here) return;
+  const int t = t0 + warp;
+  float* z = z_s + warp * e_pad;
   for (int c = 0; c < top; ++c) {
     float best = -INFINITY;
     int arg = 0x7fffffff;
     for (int e = lane; e < n_experts; e += 32) {
-      const float z = z_s[e];
-      if (z > best) { best = z; arg = e; }       // rising e within a lane: the first maximum stays
+      const float zv = z[e];
+      if (zv > best) { best = zv; arg = e; }     // rising e within a lane: the first maximum stays
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -70,7 +91,7 @@ moe_route_kernel(const T* __restrict__ x, int ld, const float* __restrict__ w_ro
     if (lane == 0) {
       choice[(size_t)t * top + c] = arg;
       score[(size_t)t * top + c] = 1.f / (1.f + expf(-best));
-      z_s[arg] = -INFINITY;
+      z[arg] = -INFINITY;
     }
     __syncwarp();
   }
@@ -235,13 +256,14 @@ ERB_EXPORT int erb_moe_route(const void* x, int ld, const float* w_router, int n
     return fail(ERB_ERR_ARG, "moe_route: %d of %d experts", top, n_experts);
   cudaStream_t s = (cudaStream_t)stream;
   const int n_pairs = n_tokens * top;
-  const size_t route_smem = sizeof(float) * ((size_t)((n_experts + 3) & ~3) + width);
+  const size_t route_smem = sizeof(float) * kRouteTokens * ((size_t)((n_experts + 3) & ~3) + width);
   if (route_smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(moe_route_kernel<elem_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem);
     if (err != cudaSuccess) return fail(ERB_ERR_CUDA, "moe_route: %s", cudaGetErrorString(err));
   }
-  launch_chained(moe_route_kernel<elem_t>, dim3(n_tokens), dim3(kRouteThreads), route_smem, s, (const elem_t*)x, ld,
-                 w_router, width, n_experts, top, choice, score);
+  if (route_smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "moe_route: rows of %d entries with %d experts", width, n_experts);
+  launch_chained(moe_route_kernel<elem_t>, dim3((n_tokens + kRouteTokens - 1) / kRouteTokens), dim3(kRouteThreads), route_smem, s,
+                 (const elem_t*)x, ld, w_router, n_tokens, width, n_experts, top, choice, score);
   int rc = check_launch("moe_route");
   if (rc) return rc;
   launch_chained(moe_lists_kernel, dim3(n_experts), dim3(256), sizeof(int) * n_experts, s, (const int*)choice, n_pairs, n_experts,
