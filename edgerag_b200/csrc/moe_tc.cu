@@ -7,7 +7,8 @@
 //   gather      (a kernel of its own, before the gate/up product) writes the rows of the lists once, in list order:
 //               xs[list row] = round(score * x[token]), so that both products read their rows as plain 2-d tiles
 //   warp 0      one thread brings tiles of the weight (2 x 128 rows x 64 k) and of the rows (MT x 64 k) into
-//               128-byte-swizzled shared memory with TMA tensor copies, several stages deep
+//               128-byte-swizzled shared memory with TMA tensor copies, five stages deep (tiles of 128 rows: two, and two
+//               blocks share an SM)
 //   warp 1      one thread issues tcgen05.mma with the weight's rows as the M = 128 side and the list's rows as the N side,
 //               once per accumulator; the accumulators are 2 x MT columns of TMEM
 //   all warps   read the accumulators (a thread = a row of the weight in each) and finish from registers:
@@ -44,7 +45,8 @@ constexpr uint32_t kWBytes = kTileN * kTileK * 2;      // 16 KB
 template <int MT> struct Plan {
   static constexpr uint32_t kABytes = MT * kTileK * 2;
   static constexpr uint32_t kStageBytes = 2 * kWBytes + kABytes;
-  static constexpr int kStages = MT >= 128 ? 4 : 5;
+  // tiles of 128 rows: two stages a block, so that two blocks share an SM and one's epilogue runs under the other's products
+  static constexpr int kStages = MT >= 128 ? 2 : 5;
   static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;
   static constexpr uint32_t kTmemCols = 2 * MT < 32 ? 32 : 2 * MT;
 };
@@ -79,7 +81,7 @@ moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const int* __res
 // grid (row tiles of the lists: an upper bound, column tiles of the weight).  GATED: the weight of an expert holds n_out
 // gate rows and then n_out up rows, a tile takes 128 of each; else it takes 256 neighbouring rows.
 template <int MT, bool GATED>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, MT >= 128 ? 2 : 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
               const int* __restrict__ offsets, const int* __restrict__ tiles, const int* __restrict__ order, int n_experts,
               int top, int n_tokens, int n_out, int K, __nv_bfloat16* __restrict__ act, float* __restrict__ parts,
@@ -290,13 +292,6 @@ int run(const void* a, const void* w, const int* offsets, const int* tiles, cons
 
 }  // namespace
 
-// Rows of a tile for `pairs` (token, choice) pairs over `n_experts` experts: the smallest of 16, 32, 64, 128 that holds an
-// expert's even share, so that few rows cost few columns of the accumulator and many rows re-read the weight seldom.
-ERB_EXPORT int erb_moe_tc_tile_rows(long long pairs, int n_experts) {
-  const long long share = (pairs + n_experts - 1) / (n_experts > 0 ? n_experts : 1);
-  return share <= 16 ? 16 : share <= 32 ? 32 : share <= 64 ? 64 : 128;
-}
-
 // xs[list row][width] = round(score[pair] * x[token of pair][:]), pair = order[list row]; bfloat16, width a multiple of 8,
 // rows 16-byte aligned.
 ERB_EXPORT int erb_moe_tc_gather(const void* x, int ldx, const int* order, const float* score, int top, int n_tokens, int width,
@@ -312,7 +307,7 @@ ERB_EXPORT int erb_moe_tc_gather(const void* x, int ldx, const int* order, const
 }
 
 // act[list row][ff] = silu(W_gate r) * (W_up r) for the rows r = xs[list row] of every expert's list; w [experts][2 ff][k]
-// (gate rows, then up rows).  tile_rows: what the lists' tile offsets were made for (erb_moe_tc_tile_rows).
+// (gate rows, then up rows).  tile_rows: what the lists' tile offsets were made for (16, 32, 64 or 128).
 ERB_EXPORT int erb_moe_tc_gate_up(const void* xs, const void* w, const int* offsets, const int* tiles, const int* order,
                                   int n_experts, int top, int n_tokens, int ff, int K, int tile_rows, void* act, int* status,
                                   void* stream) {

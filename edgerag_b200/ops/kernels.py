@@ -105,7 +105,6 @@ _SIGNATURES = {
     "erb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "erb_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_int, c_void_p],
-    "erb_moe_tc_tile_rows": [c_longlong, c_int],
     "erb_moe_tc_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "erb_moe_tc_gate_up": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                            c_void_p, c_void_p],
@@ -1134,10 +1133,10 @@ def moe_tc_supported(dtype: torch.dtype, width: int, ff: int) -> bool:
 
 def moe_tc_tile_rows(n_tokens: int, n_experts: int, top: int) -> int:
     """Rows of a tile of the tensor-core products for this many tokens: 16 to 128, the smallest that holds an expert's
-    even share of the (token, choice) pairs."""
-    fn = native.load("moe_tc", None).erb_moe_tc_tile_rows
-    fn.argtypes, fn.restype = _SIGNATURES["erb_moe_tc_tile_rows"], c_int
-    return int(fn(n_tokens * top, n_experts))
+    even share of the (token, choice) pairs, so that few rows cost few columns of the accumulator and many rows re-read
+    the weight seldom."""
+    share = -(-n_tokens * top // max(1, n_experts))
+    return 16 if share <= 16 else 32 if share <= 32 else 64 if share <= 64 else 128
 
 
 def moe_tc_gather(x: torch.Tensor, lists: torch.Tensor, score: torch.Tensor, n_experts: int, top: int, xs: torch.Tensor) -> None:

@@ -56,6 +56,8 @@ ALONE = {
     "delta": plain.make_config([DEL]),
     "delta_all_key_heads_two_taps_all_experts": plain.make_config([DEL_B], width=72),
     "delta_one_key_head_no_ffn": plain.make_config([DEL_C], width=48),
+    "delta_one_tap": plain.make_config([plain.delta_layer(heads=2, kv_heads=2, dim=32, vdim=16, conv=1, experts=1, top=1, ff=32, shared_ff=8)],
+                                       width=40),
     "chunks": plain.make_config([ATT]),
     "chunks_odd_head_sizes_full_rotation": plain.make_config([ATT_B], width=72),
     "chunks_one_kv_head_wide_values_no_ffn": plain.make_config([ATT_C], width=48),
@@ -541,6 +543,24 @@ def test_chunk_attention_with_one_key_made_dominant(case, dtype):
         k.attention_decode(qd, kp, vp, tables1, tok, pos, out1, H, 0.5, torch.empty(acc, device="cuda"), torch.empty(ml, device="cuda"),
                            splits, split_keys=split, chunk=chunk)
         check(out1, f"single tokens, splits of {split}")
+        if k.decode_gqa_supported(tdt, d, 0, H, G, page, split, splits):
+            # grouped query heads of 64 on tensor cores
+            out4 = torch.full_like(qd, float("nan"))
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            k.attention_decode_gqa(qd, kp, vp, tables1, tok, pos, out4, H, 0.5, torch.empty(acc, device="cuda"),
+                                   torch.empty(ml, device="cuda"), splits, status, split_keys=split, chunk=chunk)
+            assert int(status.item()) == 0
+            check(out4, f"grouped heads, splits of {split}")
+        if k.decode_bulk_supported(tdt, d, 0, H, G, splits):
+            # the kernel that streams pages with bulk copies: one kv head per block, and as many as it likes to group
+            for group in (1, 0):
+                out3 = torch.full_like(qd, float("nan"))
+                status = torch.zeros(1, dtype=torch.int32, device="cuda")
+                k.attention_decode_bulk(qd, kp, vp, tables1, tok, pos, out3, H, 0.5, torch.empty(acc, device="cuda"),
+                                        torch.empty(ml, device="cuda"), splits, status, split_keys=split, head_group=group,
+                                        chunk=chunk)
+                assert int(status.item()) == 0
+                check(out3, f"bulk copies, splits of {split}, group {group}")
     if k.prefill_tc_supported(tdt, d, 0, page):
         out2 = torch.full_like(qd, float("nan"))
         starts = torch.arange(n + 1, dtype=torch.int32).cuda()
