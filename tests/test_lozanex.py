@@ -422,8 +422,10 @@ def test_long_decoding_over_many_chunks(dtype, folders):
 
 
 @pytest.mark.gpu
-def test_layer_sizes_of_a_larger_model(folders):
-    """Heads of 64 and 128, a chunk longer than a split of keys, a prompt of several chunks, experts of more rows than a tile."""
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_sizes_of_a_larger_model(dtype, folders):
+    """Heads of 64 and 128, a chunk longer than a split of keys, a prompt of several chunks, experts of more rows than a tile.
+    In bfloat16 these sizes take the tensor-core kernels (portions, grouped heads, bulk copies, the experts' products)."""
     raw = plain.make_config([plain.delta_layer(heads=4, kv_heads=2, dim=64, vdim=128, conv=4, experts=8, top=2, ff=64, shared_ff=128),
                              plain.attention_layer(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=32, base=250000.0, size=600, scale=0.125,
                                                    experts=4, top=1, ff=96, shared_ff=64),
@@ -431,9 +433,10 @@ def test_layer_sizes_of_a_larger_model(folders):
                             width=128, vocab=96)
     folder, raw, tensors = folders("larger", raw, seed=3)
     toks = tokens_for(raw, 1300, 9)
-    eng = make_engine(folder, "float32", num_blocks=256, max_step_tokens=2048)
-    check_request(eng, raw, tensors, toks, [1300], "float32", "whole")
-    check_request(eng, raw, tensors, toks, [590, 2, 9, 257, 400, 30] + [1] * 12, "float32", "portions")
+    eng = make_engine(folder, dtype, num_blocks=256, max_step_tokens=2048)
+    check_request(eng, raw, tensors, toks, [1300], dtype, "whole")
+    check_request(eng, raw, tensors, toks, [590, 2, 9, 257, 400, 30] + [1] * 12, dtype, "portions")
+    check_request(eng, raw, tensors, toks[:700], [598] + [1] * 102, dtype, "decoding over a chunk's end")
 
 
 # --- kernels with inputs made so that a fault shows ---------------------------------------------------
