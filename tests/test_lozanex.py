@@ -42,6 +42,8 @@ ATT_C = plain.attention_layer(heads=6, kv_heads=1, dim=16, vdim=48, rot_dims=8, 
 ATT_SHARES = plain.attention_layer(heads=2, kv_heads=2, dim=32, vdim=32, rot_dims=12, base=700.0, size=9, scale=0.4, kv_from=1,
                                    experts=4, top=3, ff=16, shared_ff=24)
 
+#: (eps 1e-5: the closing norms make single tokens ill-conditioned where a sublayer's output is near zero; with 2e-5 the
+#: one-token request of the batch test lands on such a point, where the plain model turns weight noise of 1e-7 into 5e-3)
 FULL = plain.make_config([DEL, ATT, DEL_B, ATT_SHARES, ATT_C, DEL_C, DEL], width=80, vocab=203, eps=1e-5)
 
 
@@ -427,7 +429,7 @@ def test_layer_sizes_of_a_larger_model(dtype, folders):
     """Heads of 64 and 128, a chunk longer than a split of keys, a prompt of several chunks, experts of more rows than a tile.
     In bfloat16 these sizes take the tensor-core kernels (portions, grouped heads, bulk copies, the experts' products)."""
     raw = plain.make_config([plain.delta_layer(heads=4, kv_heads=2, dim=64, vdim=128, conv=4, experts=8, top=2, ff=64, shared_ff=128),
-                             plain.attention_layer(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=32, base=250000.0, size=600, scale=0.125,
+                             plain.attention_layer(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=32, base=300000.0, size=600, scale=0.11,
                                                    experts=4, top=1, ff=96, shared_ff=64),
                              plain.attention_layer(heads=2, kv_heads=1, dim=128, vdim=128, rot_dims=64, size=256, scale=0.09, experts=None)],
                             width=128, vocab=96)
