@@ -82,7 +82,10 @@ delta_prepare_kernel(const T* __restrict__ qkv, int channels, const T* __restric
     sk = fmaf(kv, kv, sk);
     sq = fmaf(qv, qv, sq);
   }
-  const float rk = rsqrtf(warp_sum(sk) + 1e-6f), rq = rsqrtf(warp_sum(sq) + 1e-6f) * q_scale;
+  // (the roots, the decay and the write strength once per token in double, rounded once: their errors would otherwise
+  //  compound along the recurrence)
+  const float rk = (float)(1.0 / sqrt((double)warp_sum(sk) + 1e-6));
+  const float rq = (float)((double)q_scale / sqrt((double)warp_sum(sq) + 1e-6));
   float* qd = out.qk + ((size_t)t * G + kh) * 2 * dp;
   float* kd = qd + dp;
   float kq = 0.f;
@@ -97,8 +100,9 @@ delta_prepare_kernel(const T* __restrict__ qkv, int channels, const T* __restric
   for (int r = 0; r < rep; ++r) {
     const int h = kh * rep + r;
     if (lane == 0) {
-      const float beta = 1.f / (1.f + expf(-Elem<T>::load(raw + off_b + h)));
-      const float g = expf(-expf(a_log[h]) * softplus_f(Elem<T>::load(raw + off_a + h) + dt_bias[h]));
+      const float beta = (float)(1.0 / (1.0 + exp(-(double)Elem<T>::load(raw + off_b + h))));
+      const double z = (double)(Elem<T>::load(raw + off_a + h) + dt_bias[h]);
+      const float g = (float)exp(-exp((double)a_log[h]) * (z > 30.0 ? z : log1p(exp(z))));
       *reinterpret_cast<float4*>(out.sc + ((size_t)t * H + h) * 4) = make_float4(beta, g, kq, 0.f);
     }
     const T* vs = row + 2 * G * d + h * dv;
