@@ -75,6 +75,9 @@ def _register_builtin() -> None:
     from ..models.lozanex import LozanexConfig, lozanex_plan
 
     register_architecture(["Lozanex", "lozanex"], LozanexConfig.from_dict, lozanex_plan)
+    from ..models.pudadra import PudadraConfig, pudadra_plan
+
+    register_architecture(["Pudadra", "pudadra"], PudadraConfig.from_dict, pudadra_plan)
 
 
 _register_builtin()

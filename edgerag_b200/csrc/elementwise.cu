@@ -46,7 +46,8 @@ ERB_EXPORT int erb_embed_rows(void* hidden, const void* table, const void* embed
 
 // ---------------------------------------------------------------------------------------------
 // Residual add + RMSNorm.
-//   r = hidden[row] (+ delta[row])            in float, stored back when `write_back`
+//   r = hidden[row] (+ dscale * delta[row])   in float, stored back when `write_back` (dscale: a constant of the model
+//                                             that multiplies every update of its stream; 1 for most)
 // The update may also come as `n_parts` float arrays of partial sums, `part_stride` floats apart (a
 // product whose k was split over blocks): delta = round_T(((p0 + p1) + p2) + ...), added in float in that
 // order and rounded to T once, as if the product had been stored in T like every other update.
@@ -60,7 +61,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restri
                                    const float* __restrict__ parts, int n_parts, size_t part_stride,
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden_size, float eps,
-                                   int write_back, int exact) {
+                                   int write_back, int exact, float dscale) {
   chain_wait();
   extern __shared__ float row_cache[];  // hidden_size floats, then 32 of scratch
   float* scratch = row_cache + hidden_size;
@@ -72,11 +73,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restri
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden_size; i += blockDim.x) {
     float v = h[i];
-    if (d) v += Elem<T>::load(d + i);
+    if (d) v += dscale * Elem<T>::load(d + i);
     if (ps) {
       float sum = ps[i];
       for (int sp = 1; sp < n_parts; ++sp) sum += ps[sp * part_stride + i];
-      v += Elem<T>::round(sum);
+      v += dscale * Elem<T>::round(sum);
     }
     row_cache[i] = v;
     if (write_back && (d || ps)) h[i] = v;
@@ -126,7 +127,7 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
                                         const float* __restrict__ parts, int n_parts, size_t part_stride,
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int hidden_size, float eps,
-                                        int write_back, int flags) {
+                                        int write_back, int flags, float dscale) {
   extern __shared__ float row_cache[];
   const int settled = flags & 1;
   const bool exact = flags & 2;        // the normed value is not rounded before the weight multiplies it
@@ -180,13 +181,13 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
           for (int j = 0; j < 4; ++j) dv[j] += pv[j];
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] += Elem<T>::round(dv[j]);
+        for (int j = 0; j < 4; ++j) v[j] += dscale * Elem<T>::round(dv[j]);
         if (write_back) *reinterpret_cast<float4*>(h + i) = make_float4(v[0], v[1], v[2], v[3]);
       } else if (d) {
         float dv[4];
         Pack4<T>::load(d + i, dv);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] += dv[j];
+        for (int j = 0; j < 4; ++j) v[j] += dscale * dv[j];
         if (write_back) *reinterpret_cast<float4*>(h + i) = make_float4(v[0], v[1], v[2], v[3]);
       }
       if constexpr (REGS) {
@@ -247,7 +248,7 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
 namespace {
 int run_add_rmsnorm(void* hidden, const void* delta, const float* parts, int n_parts, size_t part_stride,
                     const float* weight, void* out, const int* rows, int n_rows, int hidden_size, float eps,
-                    int write_back, int settled, void* stream) {
+                    int write_back, int settled, float dscale, void* stream) {
   if (n_rows <= 0) return ERB_OK;
   const size_t smem = (size_t)(hidden_size + 32) * sizeof(float);
   if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "add_rmsnorm: hidden_size %d too large", hidden_size);
@@ -268,7 +269,7 @@ int run_add_rmsnorm(void* hidden, const void* delta, const float* parts, int n_p
     if (one_pass) {
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, true, true>, dim3(n_rows), dim3(threads), small, (cudaStream_t)stream,
           (float*)hidden, (const elem_t*)nullptr, parts, n_parts, part_stride, weight, (elem_t*)out, rows, hidden_size, eps,
-          write_back, settled);
+          write_back, settled, dscale);
     } else {
       if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<elem_t, 1, false, true>,
@@ -277,7 +278,7 @@ int run_add_rmsnorm(void* hidden, const void* delta, const float* parts, int n_p
       }
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, false, true>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream,
           (float*)hidden, (const elem_t*)nullptr, parts, n_parts, part_stride, weight, (elem_t*)out, rows, hidden_size, eps,
-          write_back, settled);
+          write_back, settled, dscale);
     }
   } else if (vec) {
     // many rows of 2048 and more: half the threads, two virtual threads each (same sums, see the kernel)
@@ -291,19 +292,19 @@ int run_add_rmsnorm(void* hidden, const void* delta, const float* parts, int n_p
     const size_t small = 32 * sizeof(float);
     if (halve && one_pass)
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 2, true>, dim3(n_rows), dim3(256), small, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
+          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled, dscale);
     else if (halve)
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 2, false>, dim3(n_rows), dim3(256), smem, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
+          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled, dscale);
     else if (one_pass)
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, true>, dim3(n_rows), dim3(threads), small, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
+          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled, dscale);
     else
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, false>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
+          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled, dscale);
   } else {
     launch_chained(add_rmsnorm_kernel<elem_t>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
-        (const elem_t*)delta, parts, n_parts, part_stride, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled & 2);
+        (const elem_t*)delta, parts, n_parts, part_stride, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled & 2, dscale);
   }
   return check_launch("add_rmsnorm");
 }
@@ -311,57 +312,58 @@ int run_add_rmsnorm(void* hidden, const void* delta, const float* parts, int n_p
 
 ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* weight, void* out,
                                const int* rows, int n_rows, int hidden_size, float eps, int write_back,
-                               int settled, void* stream) {
-  return run_add_rmsnorm(hidden, delta, nullptr, 0, 0, weight, out, rows, n_rows, hidden_size, eps, write_back, settled, stream);
+                               int settled, float delta_scale, void* stream) {
+  return run_add_rmsnorm(hidden, delta, nullptr, 0, 0, weight, out, rows, n_rows, hidden_size, eps, write_back, settled, delta_scale,
+                         stream);
 }
 
 // The same with the update given as `n_parts` arrays of partial sums [rows of hidden][hidden_size], float,
 // `part_stride` floats from one to the next; they are added in their order.
 ERB_EXPORT int erb_add_rmsnorm_parts(void* hidden, const float* parts, int n_parts, long long part_stride, const float* weight,
                                      void* out, const int* rows, int n_rows, int hidden_size, float eps, int write_back,
-                                     int settled, void* stream) {
+                                     int settled, float delta_scale, void* stream) {
   if (!parts || n_parts < 1 || part_stride < 0) return fail(ERB_ERR_ARG, "add_rmsnorm_parts: bad arguments");
   return run_add_rmsnorm(hidden, nullptr, parts, n_parts, (size_t)part_stride, weight, out, rows, n_rows, hidden_size, eps,
-                         write_back, settled, stream);
+                         write_back, settled, delta_scale, stream);
 }
 
 // hidden[row] += delta[row] without a norm (the last residual of a stack that ends without one).
 template <typename T>
-__global__ void residual_add_kernel(float* __restrict__ hidden, const T* __restrict__ delta, size_t n) {
+__global__ void residual_add_kernel(float* __restrict__ hidden, const T* __restrict__ delta, size_t n, float dscale) {
   chain_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) hidden[i] += Elem<T>::load(delta + i);
+  if (i < n) hidden[i] += dscale * Elem<T>::load(delta + i);
 }
 
 // hidden += round_T(p0 + p1 + ...) for float partial sums, `part_stride` floats apart.
 template <typename T>
 __global__ void residual_add_parts_kernel(float* __restrict__ hidden, const float* __restrict__ parts, int n_parts,
-                                          size_t part_stride, size_t n) {
+                                          size_t part_stride, size_t n, float dscale) {
   chain_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float sum = parts[i];
   for (int sp = 1; sp < n_parts; ++sp) sum += parts[sp * part_stride + i];
-  hidden[i] += Elem<T>::round(sum);
+  hidden[i] += dscale * Elem<T>::round(sum);
 }
 
 ERB_EXPORT int erb_residual_add_parts(void* hidden, const float* parts, int n_parts, long long part_stride, long long n,
-                                      void* stream) {
+                                      float delta_scale, void* stream) {
   if (n <= 0) return ERB_OK;
   if (!parts || n_parts < 1 || part_stride < 0) return fail(ERB_ERR_ARG, "residual_add_parts: bad arguments");
   const int threads = 256;
   const unsigned blocks = (unsigned)((n + threads - 1) / threads);
   launch_chained(residual_add_parts_kernel<elem_t>, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, (float*)hidden, parts,
-      n_parts, (size_t)part_stride, (size_t)n);
+      n_parts, (size_t)part_stride, (size_t)n, delta_scale);
   return check_launch("residual_add_parts");
 }
 
-ERB_EXPORT int erb_residual_add(void* hidden, const void* delta, long long n, void* stream) {
+ERB_EXPORT int erb_residual_add(void* hidden, const void* delta, long long n, float delta_scale, void* stream) {
   if (n <= 0) return ERB_OK;
   const int threads = 256;
   const unsigned blocks = (unsigned)((n + threads - 1) / threads);
   launch_chained(residual_add_kernel<elem_t>, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, (float*)hidden,
-      (const elem_t*)delta, (size_t)n);
+      (const elem_t*)delta, (size_t)n, delta_scale);
   return check_launch("residual_add");
 }
 
@@ -1632,4 +1634,57 @@ ERB_EXPORT int erb_qkv_whole_norm(void* qkv, int ld, const float* q_bias, const 
                  k_norm, (float)q_count, (float)k_count, eps, positions, inv_freq, rot_dim, slots, (elem_t*)k_pages,
                  (elem_t*)v_pages, nq, nkv, head_dim, page_size, has_kv);
   return check_launch("qkv_whole_norm");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The activation of a feed-forward without a gate branch: out[t][i] = f(in[t][i]) for i < width, in float, rounded once.
+//   act 0: the exact gelu, 0.5 z (1 + erf(z / sqrt 2));  act 1: the square of relu.
+// `gate_col` >= 0: column `gate_col` of the input row holds one logit per token, and the row is multiplied by its sigmoid
+// (a branch that is scaled as a whole: the scale commutes with the product that follows).
+// ---------------------------------------------------------------------------------------------
+#define ERB_ACT_GELU_ERF 0
+#define ERB_ACT_RELU_SQUARED 1
+__device__ __forceinline__ float act_value(float z, int act) {
+  if (act == ERB_ACT_RELU_SQUARED) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+}
+
+template <typename T>
+__global__ void act_rows_kernel(const T* __restrict__ in, int ld_in, T* __restrict__ out, int width, int act, int gate_col) {
+  chain_wait();
+  const T* row = in + (size_t)blockIdx.x * ld_in;
+  const float g = gate_col >= 0 ? 1.f / (1.f + expf(-Elem<T>::load(row + gate_col))) : 1.f;
+  T* dst = out + (size_t)blockIdx.x * width;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < width; i += gridDim.y * blockDim.x)
+    Elem<T>::store(dst + i, act_value(Elem<T>::load(row + i), act) * g);
+}
+
+ERB_EXPORT int erb_act_rows(const void* in, int ld_in, void* out, int n_rows, int width, int act, int gate_col, void* stream) {
+  if (n_rows <= 0 || width <= 0) return ERB_OK;
+  if (ld_in < width || gate_col >= ld_in || (act != ERB_ACT_GELU_ERF && act != ERB_ACT_RELU_SQUARED))
+    return fail(ERB_ERR_ARG, "act_rows: bad sizes or activation %d", act);
+  int y = (width + 1023) / 1024;
+  if (y > 64) y = 64;
+  launch_chained(act_rows_kernel<elem_t>, dim3(n_rows, y), dim3(256), 0, (cudaStream_t)stream, (const elem_t*)in, ld_in,
+                 (elem_t*)out, width, act, gate_col);
+  return check_launch("act_rows");
+}
+
+// Float rows times a constant, in place (logits of a head whose model scales them); rows `stride` floats apart.
+__global__ void scale_rows_kernel(float* __restrict__ x, int width, int stride, float scale) {
+  chain_wait();
+  float* row = x + (size_t)blockIdx.x * stride;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < width; i += gridDim.y * blockDim.x) row[i] *= scale;
+}
+
+ERB_EXPORT int erb_scale_rows(float* x, int n_rows, int width, int stride, float scale, void* stream) {
+  if (n_rows <= 0 || width <= 0) return ERB_OK;
+  if (stride < width) return fail(ERB_ERR_ARG, "scale_rows: the stride must cover a row");
+  int y = (width + 1023) / 1024;
+  if (y > 64) y = 64;
+  launch_chained(scale_rows_kernel, dim3(n_rows, y), dim3(256), 0, (cudaStream_t)stream, x, width, stride, scale);
+  return check_launch("scale_rows");
 }

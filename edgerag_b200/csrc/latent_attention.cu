@@ -140,7 +140,7 @@ latent_attention_kernel(const float* __restrict__ q_lat, const T* __restrict__ p
                         int max_pages, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                         const T* __restrict__ gate, int gate_ld, const float* __restrict__ sink, T* __restrict__ out,
                         float* __restrict__ part, int first_token, int n_rows, int H, int R, int Dk, int page_size,
-                        int split_keys, int n_splits, float scale) {
+                        int split_keys, int n_splits, float scale, int window) {
   chain_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kLatWarps + warp;
@@ -148,8 +148,11 @@ latent_attention_kernel(const float* __restrict__ q_lat, const T* __restrict__ p
   const int split = blockIdx.y;
   const int t = first_token + row / H, h = row % H;
   const int seq = seq_of_token[t], pos = positions[t];
-  const int begin = n_splits > 1 ? split * split_keys : 0;
-  const int end = n_splits > 1 ? min(pos + 1, begin + split_keys) : pos + 1;
+  // a window moves the first key; the splits stay at multiples of their size, counted from the one that holds it
+  const int lo = first_visible_key(pos, window);
+  const int base = n_splits > 1 ? (lo / split_keys + split) * split_keys : 0;
+  const int begin = n_splits > 1 ? max(lo, base) : lo;
+  const int end = n_splits > 1 ? min(pos + 1, base + split_keys) : pos + 1;
 
   float2 q[NI], acc[NI];
   const float* q_row = q_lat + ((size_t)t * H + h) * Dk;
@@ -318,7 +321,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
                             const int* __restrict__ positions, const __nv_bfloat16* __restrict__ gate, int gate_ld,
                             const float* __restrict__ sink, __nv_bfloat16* __restrict__ out, float* __restrict__ part,
                             int first_token, int seq0, int n_seqs, int H, int R, int Dk, int page_size, int split_keys,
-                            int n_splits, float scale) {
+                            int n_splits, float scale, int window) {
   chain_wait();
   constexpr int M = 16 * MT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -345,8 +348,11 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
   const int valid = min(M, rows_s - r0);
   const int pos_max = positions[tok0 + (r0 + valid - 1) / H];
   const int split = blockIdx.y;
-  const int begin = n_splits > 1 ? split * split_keys : 0;
-  const int end = n_splits > 1 ? min(pos_max + 1, begin + split_keys) : pos_max + 1;
+  // the first key any row of the block sees (its first row's window); splits are counted from the one that holds it
+  const int lo = first_visible_key(positions[tok0 + r0 / H], window);
+  const int base = n_splits > 1 ? (lo / split_keys + split) * split_keys : 0;
+  const int begin = n_splits > 1 ? max(lo, base) : lo;
+  const int end = n_splits > 1 ? min(pos_max + 1, base + split_keys) : pos_max + 1;
   const int* bt = block_tables + (size_t)s * max_pages;
   const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
@@ -462,9 +468,10 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
     for (int q = 0; q < QM; ++q)
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const int lim = min(W == 16 ? (mt0 ? pos_r[MT - 1][j] : pos_r[0][j]) : pos_r[q][j], end - 1);
-        if (key0 > lim) sc[q][2 * j] = -INFINITY;
-        if (key0 + 1 > lim) sc[q][2 * j + 1] = -INFINITY;
+        const int pos_row = W == 16 ? (mt0 ? pos_r[MT - 1][j] : pos_r[0][j]) : pos_r[q][j];
+        const int lim = min(pos_row, end - 1), low = first_visible_key(pos_row, window);
+        if (key0 > lim || key0 < low) sc[q][2 * j] = -INFINITY;
+        if (key0 + 1 > lim || key0 + 1 < low) sc[q][2 * j + 1] = -INFINITY;
         float mx = fmaxf(sc[q][2 * j], sc[q][2 * j + 1]);
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -578,10 +585,10 @@ template <int NI>
 void launch_attention(dim3 grid, cudaStream_t stream, const float* q_lat, const elem_t* pages, const int* block_tables,
                       int max_pages, const int* seq_of_token, const int* positions, const elem_t* gate, int gate_ld,
                       const float* sink, elem_t* out, float* part, int first_token, int n_rows, int H, int R, int Dk,
-                      int page_size, int split_keys, int n_splits, float scale) {
+                      int page_size, int split_keys, int n_splits, float scale, int window) {
   launch_chained(latent_attention_kernel<elem_t, NI>, grid, dim3(kLatWarps * 32), 0, stream, q_lat, pages, block_tables,
                  max_pages, seq_of_token, positions, gate, gate_ld, sink, out, part, first_token, n_rows, H, R, Dk, page_size,
-                 split_keys, n_splits, scale);
+                 split_keys, n_splits, scale, window);
 }
 
 }  // namespace
@@ -617,8 +624,10 @@ ERB_EXPORT int erb_latent_q_rotate(const void* q, int n_tokens, int ld, int H, i
 ERB_EXPORT int erb_latent_attention(const float* q_lat, const void* pages, const int* block_tables, int max_pages,
                                     const int* seq_of_token, const int* positions, const void* gate, int gate_ld,
                                     const float* sink, void* out, float* part, int first_token, int n_tokens, int H, int R,
-                                    int dr, int page_size, int split_keys, int n_splits, float scale, void* stream) {
+                                    int dr, int page_size, int split_keys, int n_splits, float scale, int window,
+                                    void* stream) {
   if (n_tokens <= 0) return ERB_OK;
+  if (window < 0) return fail(ERB_ERR_ARG, "latent_attention: a window is 0 (none) or positive");
   const int Dk = R + dr;
   if (H <= 0 || R <= 0 || R % 2 || dr % 2 || page_size <= 0 || n_splits < 1 || n_splits > kCombineSplits ||
       (n_splits > 1 && (!part || split_keys <= 0)))
@@ -628,7 +637,7 @@ ERB_EXPORT int erb_latent_attention(const float* q_lat, const void* pages, const
   const dim3 grid((n_rows + kLatWarps - 1) / kLatWarps, n_splits);
   cudaStream_t st = (cudaStream_t)stream;
 #define ERB_LAT(NI) launch_attention<NI>(grid, st, q_lat, (const elem_t*)pages, block_tables, max_pages, seq_of_token, positions, \
-    (const elem_t*)gate, gate_ld, sink, (elem_t*)out, part, first_token, n_rows, H, R, Dk, page_size, split_keys, n_splits, scale)
+    (const elem_t*)gate, gate_ld, sink, (elem_t*)out, part, first_token, n_rows, H, R, Dk, page_size, split_keys, n_splits, scale, window)
   if (Dk <= 128) ERB_LAT(2);
   else if (Dk <= 256) ERB_LAT(4);
   else if (Dk <= 384) ERB_LAT(6);
@@ -649,9 +658,10 @@ ERB_EXPORT int erb_latent_attention_mma(const float* q_lat, const void* pages, c
                                         const int* seq_starts, const int* positions, const void* gate, int gate_ld,
                                         const float* sink, void* out, float* part, int first_token, int seq0, int n_seqs,
                                         int n_tiles, int mt, int H, int R, int dr, int page_size, int split_keys,
-                                        int n_splits, float scale, void* stream) {
+                                        int n_splits, float scale, int window, void* stream) {
 #if ERB_ELEM == 1
   if (n_seqs <= 0 || n_tiles <= 0) return ERB_OK;
+  if (window < 0) return fail(ERB_ERR_ARG, "latent_attention_mma: a window is 0 (none) or positive");
   const int Dk = R + dr;
   if (H <= 0 || R <= 0 || R % 8 || Dk % 8 || R > 512 || page_size <= 0 || n_splits < 1 || (mt != 1 && mt != 2) ||
       ((uintptr_t)pages & 15) || (n_splits > 1 && (!part || split_keys <= 0 || split_keys % kMmaKeys)))
@@ -671,7 +681,7 @@ ERB_EXPORT int erb_latent_attention_mma(const float* q_lat, const void* pages, c
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "latent_attention_mma: %s", cudaGetErrorString(e));                   \
     launch_chained(kern, grid, dim3(W_ * 32), smem, st, q_lat, (const __nv_bfloat16*)pages, block_tables, max_pages,      \
                    seq_starts, positions, (const __nv_bfloat16*)gate, gate_ld, sink, (__nv_bfloat16*)out, part, first_token, \
-                   seq0, n_seqs, H, R, Dk, page_size, split_keys, n_splits, scale);                                       \
+                   seq0, n_seqs, H, R, Dk, page_size, split_keys, n_splits, scale, window);                               \
   } while (0)
   if (mt == 1) { if (nt <= 2) ERB_LAT_MMA(1, 2, 8); else if (nt <= 4) ERB_LAT_MMA(1, 4, 8); else ERB_LAT_MMA(1, 8, 8); }
   else { if (nt <= 2) ERB_LAT_MMA(2, 2, 16); else ERB_LAT_MMA(2, 4, 16); }

@@ -17,6 +17,15 @@ using namespace erb;
 
 ERB_DEFINE_LAST_ERROR(erb_last_error)
 
+// how a router turns logits into scores
+#define ERB_SCORE_SIGMOID 0
+#define ERB_SCORE_SOFTMAX 1
+// what a product of the experts does: the down product, the gated pair of products, a single product with an activation
+#define ERB_MOE_DOWN 0
+#define ERB_MOE_GATED 1
+#define ERB_MOE_SINGLE 2
+#define ERB_ACT_RELU_SQUARED 1
+
 namespace {
 
 constexpr int kRouteThreads = 512;
@@ -28,11 +37,12 @@ constexpr int kRouteTokens = 4;
 template <typename T>
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const T* __restrict__ x, int ld, const float* __restrict__ w_router, int n_tokens, int width, int n_experts,
-                 int top, int* __restrict__ choice, float* __restrict__ score) {
+                 int top, int* __restrict__ choice, float* __restrict__ score, int score_kind, int n_groups, int keep_groups) {
   chain_wait();
-  extern __shared__ float z_s[];                 // [kRouteTokens][n_experts padded to 4], then [kRouteTokens][width]
-  const int e_pad = (n_experts + 3) & ~3;
-  float* x_s = z_s + kRouteTokens * e_pad;
+  extern __shared__ float z_s[];                 // [kRouteTokens][n_experts padded to 4] logits, the same again for the
+  const int e_pad = (n_experts + 3) & ~3;        // groups' maxima, then [kRouteTokens][width]
+  float* g_s = z_s + kRouteTokens * e_pad;
+  float* x_s = g_s + kRouteTokens * e_pad;
   const int t0 = blockIdx.x * kRouteTokens, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n_here = min(kRouteTokens, n_tokens - t0);
 #pragma unroll
@@ -75,6 +85,47 @@ moe_route_kernel(const T* __restrict__ x, int ld, const float* __restrict__ w_ro
   if (warp >= n_here) return;
   const int t = t0 + warp;
   float* z = z_s + warp * e_pad;
+  // softmax scores: the maximum and the denominator over all experts, before any expert is ruled out
+  float z_top = 0.f, denom = 1.f;
+  if (score_kind == ERB_SCORE_SOFTMAX) {
+    float mx = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, z[e]);
+    z_top = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < n_experts; e += 32) sum += expf(z[e] - z_top);
+    denom = warp_sum(sum);
+  }
+  // groups of neighbouring experts: a group's score is its largest logit (the scores rise with the logits); the experts
+  // of all but the `keep_groups` best groups are ruled out (the lower group wins a tie)
+  if (n_groups > 1 && keep_groups < n_groups) {
+    float* gm = g_s + warp * e_pad;
+    const int per = n_experts / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      float mx = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) mx = fmaxf(mx, z[e]);
+      gm[g] = mx;
+    }
+    __syncwarp();
+    for (int c = 0; c < keep_groups; ++c) {
+      float best = -INFINITY;
+      int arg = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32) {
+        const float v = gm[g];
+        if (v > best) { best = v; arg = g; }     // (a group already kept holds NaN: never greater)
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+      }
+      if (lane == 0 && arg < n_groups) gm[arg] = __int_as_float(0x7fc00000);
+      __syncwarp();
+    }
+    for (int e = lane; e < n_experts; e += 32)
+      if (gm[e / per] == gm[e / per]) z[e] = -INFINITY;       // not NaN: the group was not kept
+    __syncwarp();
+  }
   for (int c = 0; c < top; ++c) {
     float best = -INFINITY;
     int arg = 0x7fffffff;
@@ -90,7 +141,7 @@ moe_route_kernel(const T* __restrict__ x, int ld, const float* __restrict__ w_ro
     }
     if (lane == 0) {
       choice[(size_t)t * top + c] = arg;
-      score[(size_t)t * top + c] = 1.f / (1.f + expf(-best));
+      score[(size_t)t * top + c] = score_kind == ERB_SCORE_SOFTMAX ? expf(best - z_top) / denom : 1.f / (1.f + expf(-best));
       z[arg] = -INFINITY;
     }
     __syncwarp();
@@ -151,18 +202,21 @@ __global__ void __launch_bounds__(256) moe_lists_kernel(const int* __restrict__ 
 // ---------------------------------------------------------------------------------------------
 // The experts' products on CUDA cores: a block owns TM rows of one expert's list and TN columns; k is walked in
 // steps of BK in rising order with one float accumulator per output.
-//   GATED: rows are gathered and scaled inputs, the weight holds `n_out` gate rows followed by `n_out` up rows, the
-//          output is silu(gate) * up in T at the row's place in the list;
-//   else:  rows are the list's rows of `a`, the output is float at [choice][token][:].
+//   GATED:  rows are gathered inputs (times the pair's score where `score` is given, rounded to T once), the weight holds
+//           `n_out` gate rows followed by `n_out` up rows, the output is silu(gate) * up in T at the row's place in the list;
+//   SINGLE: the same rows against `n_out` rows of one weight, the output is act(product) in T (act: the square of relu);
+//   DOWN:   rows are the list's rows of `a`, the output is float at [choice][token][:], times the pair's score where
+//           `score` is given (an expert's output weighted by its score).
 // ---------------------------------------------------------------------------------------------
 constexpr int kTM = 32, kTN = 64, kBK = 32;
 
-template <typename T, bool GATED>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weights, const int* __restrict__ offsets,
                    const int* __restrict__ tiles, const int* __restrict__ order, const float* __restrict__ score, int n_experts,
                    int top, int n_tokens, int n_out, int k_dim, T* __restrict__ act, float* __restrict__ parts) {
   chain_wait();
+  constexpr bool GATED = MODE == ERB_MOE_GATED, GATHER = MODE != ERB_MOE_DOWN;
   __shared__ float a_s[kTM][kBK + 1];
   __shared__ float b_s[kTN][kBK + 1];
   __shared__ float b2_s[GATED ? kTN : 1][kBK + 1];
@@ -186,7 +240,7 @@ moe_product_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weigh
     const int r = threadIdx.x;
     const int pair = r < n_rows ? order[row0 + r] : -1;
     pair_s[r] = pair;
-    scale_s[r] = (GATED && pair >= 0) ? score[pair] : 1.f;
+    scale_s[r] = (score && pair >= 0) ? score[pair] : 1.f;
   }
   __syncthreads();
   const T* w = weights + (size_t)e * (GATED ? 2 : 1) * n_out * k_dim;
@@ -197,7 +251,7 @@ moe_product_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weigh
       const int r = idx / kBK, kk = idx % kBK;
       float v = 0.f;
       if (r < n_rows && k0 + kk < k_dim) {
-        if (GATED) v = Elem<T>::round(scale_s[r] * Elem<T>::load(a + (size_t)(pair_s[r] / top) * lda + k0 + kk));
+        if (GATHER) v = Elem<T>::round(scale_s[r] * Elem<T>::load(a + (size_t)(pair_s[r] / top) * lda + k0 + kk));
         else v = Elem<T>::load(a + (size_t)(row0 + r) * lda + k0 + kk);
       }
       a_s[r][kk] = v;
@@ -236,9 +290,12 @@ moe_product_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weigh
       if (c >= n_out) continue;
       if (GATED) {
         Elem<T>::store(act + (size_t)(row0 + r) * n_out + c, silu_mul(acc[i][j], acc2[i][j]));
+      } else if (MODE == ERB_MOE_SINGLE) {
+        const float z = fmaxf(acc[i][j], 0.f);
+        Elem<T>::store(act + (size_t)(row0 + r) * n_out + c, z * z);
       } else {
         const int pair = pair_s[r];
-        parts[((size_t)(pair % top) * n_tokens + pair / top) * n_out + c] = acc[i][j];
+        parts[((size_t)(pair % top) * n_tokens + pair / top) * n_out + c] = acc[i][j] * scale_s[r];
       }
     }
   }
@@ -250,20 +307,24 @@ ERB_EXPORT int erb_moe_tile_rows() { return kTM; }
 
 ERB_EXPORT int erb_moe_route(const void* x, int ld, const float* w_router, int n_tokens, int width, int n_experts, int top,
                              int* choice, float* score, int* counts, int* offsets, int* tiles, int* order, int tile_rows,
-                             void* stream) {
+                             int score_kind, int n_groups, int keep_groups, void* stream) {
   if (n_tokens <= 0) return ERB_OK;
   if (width <= 0 || n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 8192)
     return fail(ERB_ERR_ARG, "moe_route: %d of %d experts", top, n_experts);
+  if ((score_kind != ERB_SCORE_SIGMOID && score_kind != ERB_SCORE_SOFTMAX) || n_groups < 1 || n_experts % n_groups ||
+      keep_groups < 1 || keep_groups > n_groups || top > keep_groups * (n_experts / n_groups))
+    return fail(ERB_ERR_ARG, "moe_route: %d groups of which %d are kept cannot give %d of %d experts", n_groups, keep_groups, top,
+                n_experts);
   cudaStream_t s = (cudaStream_t)stream;
   const int n_pairs = n_tokens * top;
-  const size_t route_smem = sizeof(float) * kRouteTokens * ((size_t)((n_experts + 3) & ~3) + width);
+  const size_t route_smem = sizeof(float) * kRouteTokens * (2 * (size_t)((n_experts + 3) & ~3) + width);
   if (route_smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(moe_route_kernel<elem_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem);
     if (err != cudaSuccess) return fail(ERB_ERR_CUDA, "moe_route: %s", cudaGetErrorString(err));
   }
   if (route_smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "moe_route: rows of %d entries with %d experts", width, n_experts);
   launch_chained(moe_route_kernel<elem_t>, dim3((n_tokens + kRouteTokens - 1) / kRouteTokens), dim3(kRouteThreads), route_smem, s,
-                 (const elem_t*)x, ld, w_router, n_tokens, width, n_experts, top, choice, score);
+                 (const elem_t*)x, ld, w_router, n_tokens, width, n_experts, top, choice, score, score_kind, n_groups, keep_groups);
   int rc = check_launch("moe_route");
   if (rc) return rc;
   launch_chained(moe_lists_kernel, dim3(n_experts), dim3(256), sizeof(int) * n_experts, s, (const int*)choice, n_pairs, n_experts,
@@ -271,20 +332,25 @@ ERB_EXPORT int erb_moe_route(const void* x, int ld, const float* w_router, int n
   return check_launch("moe_lists");
 }
 
-// gated != 0: act[list row][n_out] = silu(gate) * up from x (gathered, scaled); else parts[choice][token][n_out] from act rows.
+// mode 1 (gated): act[list row][n_out] = silu(gate) * up from x (gathered, scaled by `score` if given); mode 2 (single):
+// act[list row][n_out] = relu(up)^2 from x; mode 0 (down): parts[choice][token][n_out] from act rows, times `score` if given.
 ERB_EXPORT int erb_moe_product(const void* a, int lda, const void* weights, const int* offsets, const int* tiles,
                                const int* order, const float* score, int n_experts, int top, int n_tokens, int n_out, int k_dim,
-                               int gated, void* act, float* parts, void* stream) {
+                               int mode, void* act, float* parts, void* stream) {
   if (n_tokens <= 0) return ERB_OK;
-  if (n_out <= 0 || k_dim <= 0 || n_experts <= 0 || top <= 0) return fail(ERB_ERR_ARG, "moe_product: bad sizes");
+  if (n_out <= 0 || k_dim <= 0 || n_experts <= 0 || top <= 0 || mode < 0 || mode > 2) return fail(ERB_ERR_ARG, "moe_product: bad sizes");
   const int max_tiles = (n_tokens * top + kTM - 1) / kTM + n_experts;
   dim3 grid(max_tiles, (n_out + kTN - 1) / kTN);
-  if (gated)
-    launch_chained(moe_product_kernel<elem_t, true>, grid, dim3(256), 0, (cudaStream_t)stream, (const elem_t*)a, lda,
+  if (mode == ERB_MOE_SINGLE)
+    launch_chained(moe_product_kernel<elem_t, ERB_MOE_SINGLE>, grid, dim3(256), 0, (cudaStream_t)stream, (const elem_t*)a, lda,
+                   (const elem_t*)weights, offsets, tiles, order, score, n_experts, top, n_tokens, n_out, k_dim, (elem_t*)act,
+                   parts);
+  else if (mode == ERB_MOE_GATED)
+    launch_chained(moe_product_kernel<elem_t, ERB_MOE_GATED>, grid, dim3(256), 0, (cudaStream_t)stream, (const elem_t*)a, lda,
                    (const elem_t*)weights, offsets, tiles, order, score, n_experts, top, n_tokens, n_out, k_dim, (elem_t*)act,
                    parts);
   else
-    launch_chained(moe_product_kernel<elem_t, false>, grid, dim3(256), 0, (cudaStream_t)stream, (const elem_t*)a, lda,
+    launch_chained(moe_product_kernel<elem_t, ERB_MOE_DOWN>, grid, dim3(256), 0, (cudaStream_t)stream, (const elem_t*)a, lda,
                    (const elem_t*)weights, offsets, tiles, order, score, n_experts, top, n_tokens, n_out, k_dim, (elem_t*)act,
                    parts);
   return check_launch("moe_product");

@@ -15,7 +15,9 @@
 //               gate/up: the first accumulator holds 128 gate rows, the second the 128 up rows that go with them:
 //                        act[list row][column] = silu(gate) * up;
 //               down:    parts[choice][token][column] = the float sums (columns n0 + thread and n0 + 128 + thread),
-//                        one partial result per choice of a token
+//                        one partial result per choice of a token, times the pair's score where the expert's output
+//                        (not its input) carries the weight;
+//               single:  one product without a gate branch, act[list row][column] = relu(sum)^2 for both accumulators
 //
 // A tile's rows past the end of its expert's list are rows of the next expert (or nothing): they are multiplied along and
 // never stored.  A tile of weight rows past the expert's last row reads the next expert's rows: not stored either.  k is
@@ -67,7 +69,7 @@ moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const int* __res
        idx += (long long)gridDim.x * blockDim.x) {
     const int row = (int)(idx / per_row), c = (int)(idx % per_row);
     const int pair = order[row];
-    const float s = score[pair];
+    const float s = score ? score[pair] : 1.f;
     const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(pair / top) * ldx + c * 8);
     const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(&raw);
     uint4 packed;
@@ -80,12 +82,14 @@ moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const int* __res
 
 // grid (row tiles of the lists: an upper bound, column tiles of the weight).  GATED: the weight of an expert holds n_out
 // gate rows and then n_out up rows, a tile takes 128 of each; else it takes 256 neighbouring rows.
-template <int MT, bool GATED>
+constexpr int kDown = 0, kGated = 1, kSingle = 2;
+template <int MT, int MODE>
 __global__ void __launch_bounds__(kThreads, MT >= 128 ? 2 : 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
               const int* __restrict__ offsets, const int* __restrict__ tiles, const int* __restrict__ order, int n_experts,
               int top, int n_tokens, int n_out, int K, __nv_bfloat16* __restrict__ act, float* __restrict__ parts,
-              int* __restrict__ status) {
+              const float* __restrict__ out_score, int* __restrict__ status) {
+  constexpr bool GATED = MODE == kGated, PAIRS = MODE == kDown;
   using P = Plan<MT>;
   constexpr int kStages = P::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -134,8 +138,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     mbar_init_fence();
     for (int i = 0; i < ahead; ++i) ask(i);
   }
-  if (!GATED && tid < MT) pair_s[tid] = tid < n_rows ? order[row0 + tid] : -1;
-  if (!GATED && MT > kThreads) {
+  if (PAIRS && tid < MT) pair_s[tid] = tid < n_rows ? order[row0 + tid] : -1;
+  if (PAIRS && MT > kThreads) {
     for (int r = kThreads + tid; r < MT; r += kThreads) pair_s[r] = r < n_rows ? order[row0 + r] : -1;
   }
   if (warp == 1) {
@@ -206,11 +210,16 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         if (m >= n_rows) break;
         if (GATED) {
           if (n_a < n_out) act[(size_t)(row0 + m) * n_out + n_a] = __float2bfloat16_rn(silu_mul(v0[i], v1[i]));
+        } else if (MODE == kSingle) {
+          const float za = fmaxf(v0[i], 0.f), zb = fmaxf(v1[i], 0.f);
+          if (n_a < n_out) act[(size_t)(row0 + m) * n_out + n_a] = __float2bfloat16_rn(za * za);
+          if (n_b < n_out) act[(size_t)(row0 + m) * n_out + n_b] = __float2bfloat16_rn(zb * zb);
         } else {
           const int pair = pair_s[m];
+          const float sc = out_score ? out_score[pair] : 1.f;
           float* dst = parts + ((size_t)(pair % top) * n_tokens + pair / top) * n_out;
-          if (n_a < n_out) dst[n_a] = v0[i];
-          if (n_b < n_out) dst[n_b] = v1[i];
+          if (n_a < n_out) dst[n_a] = v0[i] * sc;
+          if (n_b < n_out) dst[n_b] = v1[i] * sc;
         }
       }
     }
@@ -247,10 +256,12 @@ int matrix_map(CUtensorMap* out, const void* p, long long rows, int K, int ld, i
   return ERB_OK;
 }
 
-template <int MT, bool GATED>
+template <int MT, int MODE>
 int launch(const CUtensorMap& mw, const CUtensorMap& ma, const int* offsets, const int* tiles, const int* order, int n_experts,
-           int top, int n_tokens, int n_out, int K, void* act, float* parts, int* status, cudaStream_t stream) {
-  auto kern = moe_tc_kernel<MT, GATED>;
+           int top, int n_tokens, int n_out, int K, void* act, float* parts, const float* out_score, int* status,
+           cudaStream_t stream) {
+  constexpr bool GATED = MODE == kGated;
+  auto kern = moe_tc_kernel<MT, MODE>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Plan<MT>::kSmemBytes);
@@ -262,13 +273,14 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const int* offsets, con
   // an upper bound of the row tiles: every expert's last tile may be short
   const dim3 grid((unsigned)((pairs + MT - 1) / MT + n_experts), (unsigned)((n_out + per_tile - 1) / per_tile));
   launch_chained(kern, grid, dim3(kThreads), Plan<MT>::kSmemBytes, stream, mw, ma, offsets, tiles, order, n_experts, top, n_tokens,
-                 n_out, K, (__nv_bfloat16*)act, parts, status);
+                 n_out, K, (__nv_bfloat16*)act, parts, out_score, status);
   return check_launch("moe_tc");
 }
 
-template <bool GATED>
+template <int MODE>
 int run(const void* a, const void* w, const int* offsets, const int* tiles, const int* order, int n_experts, int top, int n_tokens,
-        int n_out, int K, int tile_rows, void* act, float* parts, int* status, cudaStream_t stream) {
+        int n_out, int K, int tile_rows, void* act, float* parts, const float* out_score, int* status, cudaStream_t stream) {
+  constexpr bool GATED = MODE == kGated;
   if (n_tokens <= 0) return ERB_OK;
   if (n_out <= 0 || K <= 0 || n_experts <= 0 || top <= 0) return fail(ERB_ERR_ARG, "moe_tc: bad sizes");
   if ((K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15))
@@ -279,7 +291,7 @@ int run(const void* a, const void* w, const int* offsets, const int* tiles, cons
   int rc;
   if ((rc = matrix_map(&mw, w, w_rows, K, K, kTileN)) || (rc = matrix_map(&ma, a, pairs, K, K, tile_rows))) return rc;
 #define ERB_MOE_CASE(MT) \
-  case MT: return launch<MT, GATED>(mw, ma, offsets, tiles, order, n_experts, top, n_tokens, n_out, K, act, parts, status, stream);
+  case MT: return launch<MT, MODE>(mw, ma, offsets, tiles, order, n_experts, top, n_tokens, n_out, K, act, parts, out_score, status, stream);
   switch (tile_rows) {
     ERB_MOE_CASE(16)
     ERB_MOE_CASE(32)
@@ -311,14 +323,23 @@ ERB_EXPORT int erb_moe_tc_gather(const void* x, int ldx, const int* order, const
 ERB_EXPORT int erb_moe_tc_gate_up(const void* xs, const void* w, const int* offsets, const int* tiles, const int* order,
                                   int n_experts, int top, int n_tokens, int ff, int K, int tile_rows, void* act, int* status,
                                   void* stream) {
-  return run<true>(xs, w, offsets, tiles, order, n_experts, top, n_tokens, ff, K, tile_rows, act, nullptr, status, (cudaStream_t)stream);
+  return run<kGated>(xs, w, offsets, tiles, order, n_experts, top, n_tokens, ff, K, tile_rows, act, nullptr, nullptr, status,
+                     (cudaStream_t)stream);
 }
 
-// parts[choice][token][width] (float) = W_down act[list row]; w [experts][width][ff].
+// act[list row][ff] = relu(W_up r)^2 for the rows r = xs[list row] of every expert's list; w [experts][ff][k].
+ERB_EXPORT int erb_moe_tc_up_act(const void* xs, const void* w, const int* offsets, const int* tiles, const int* order,
+                                 int n_experts, int top, int n_tokens, int ff, int K, int tile_rows, void* act, int* status,
+                                 void* stream) {
+  return run<kSingle>(xs, w, offsets, tiles, order, n_experts, top, n_tokens, ff, K, tile_rows, act, nullptr, nullptr, status,
+                      (cudaStream_t)stream);
+}
+
+// parts[choice][token][width] (float) = W_down act[list row] (times out_score[pair] where given); w [experts][width][ff].
 ERB_EXPORT int erb_moe_tc_down(const void* act, const void* w, const int* offsets, const int* tiles, const int* order,
-                               int n_experts, int top, int n_tokens, int width, int K, int tile_rows, float* parts, int* status,
-                               void* stream) {
+                               int n_experts, int top, int n_tokens, int width, int K, int tile_rows, float* parts,
+                               const float* out_score, int* status, void* stream) {
   if (((uintptr_t)parts & 15)) return fail(ERB_ERR_ARG, "moe_tc_down: parts must be 16-byte aligned");
-  return run<false>(act, w, offsets, tiles, order, n_experts, top, n_tokens, width, K, tile_rows, nullptr, parts, status,
+  return run<kDown>(act, w, offsets, tiles, order, n_experts, top, n_tokens, width, K, tile_rows, nullptr, parts, out_score, status,
                     (cudaStream_t)stream);
 }

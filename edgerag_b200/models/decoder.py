@@ -77,17 +77,20 @@ class DecoderModel:
             if layer is None:
                 raise ValueError(f"cache layer {cl} is read but never written")
             spec = self.blocks[layer].mixer.cache_spec()
-            if isinstance(spec, KVGroupSpec):
-                key = (spec.n_kv_heads, spec.head_dim, spec.window, spec.v_head_dim, spec.keep_first)
-                if key not in keys:
-                    keys.append(key)
-                    counts.append(0)
-                g = keys.index(key)
-                layout.placement[cl] = (g, counts[g])
-                counts[g] += 1
-            elif spec:
-                for st in spec:
-                    layout.states.append(StateSpec(f"{st.name}@{cl}", tuple(st.shape), st.dtype))
+            # pages, state records, or (a list of) both: a mixer may keep paged keys and a record of fixed size
+            for item in ([spec] if isinstance(spec, KVGroupSpec) else list(spec or [])):
+                if isinstance(item, KVGroupSpec):
+                    if layout.placement[cl] is not None:
+                        raise ValueError(f"layer {layer}: a mixer keeps one group of pages at most")
+                    key = (item.n_kv_heads, item.head_dim, item.window, item.v_head_dim, item.keep_first)
+                    if key not in keys:
+                        keys.append(key)
+                        counts.append(0)
+                    g = keys.index(key)
+                    layout.placement[cl] = (g, counts[g])
+                    counts[g] += 1
+                else:
+                    layout.states.append(StateSpec(f"{item.name}@{cl}", tuple(item.shape), item.dtype))
         layout.groups = [KVGroupSpec(c, *k) for k, c in zip(keys, counts)]
         return layout
 

@@ -26,8 +26,10 @@ _SIGNATURES = {
     "erb_embed_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                        c_void_p, c_float, c_void_p],
     "erb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int,
-                        c_void_p],
-    "erb_residual_add": [c_void_p, c_void_p, c_longlong, c_void_p],
+                        c_float, c_void_p],
+    "erb_residual_add": [c_void_p, c_void_p, c_longlong, c_float, c_void_p],
+    "erb_act_rows": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_scale_rows": [c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "erb_rope_cache_write": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_swiglu": [c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -46,9 +48,9 @@ _SIGNATURES = {
     "erb_linear_trials": [],
     "erb_linear_tc_parts": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_tc_parts_count": [c_int, c_int],
-    "erb_residual_add_parts": [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p],
+    "erb_residual_add_parts": [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_float, c_void_p],
     "erb_add_rmsnorm_parts": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
-                              c_int, c_int, c_void_p],
+                              c_int, c_int, c_float, c_void_p],
     "erb_linear_tc_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_tc_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
@@ -82,11 +84,17 @@ _SIGNATURES = {
                             c_void_p],
     "erb_latent_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                             c_void_p],
+                             c_int, c_void_p],
     "erb_latent_attention_mma": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                 c_int, c_int, c_float, c_void_p],
+                                 c_int, c_int, c_float, c_int, c_void_p],
     "erb_latent_combine": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_diff_part_floats": [c_int],
+    "erb_diff_prepare": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                         c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "erb_diff_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_float,
+                           c_void_p],
     "erb_conv_silu": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p],
     "erb_conv_state_update": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -104,12 +112,14 @@ _SIGNATURES = {
                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "erb_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                      c_void_p, c_void_p, c_int, c_void_p],
+                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "erb_moe_tc_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "erb_moe_tc_gate_up": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                            c_void_p, c_void_p],
     "erb_moe_tc_down": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                        c_void_p, c_void_p],
+                        c_void_p, c_void_p, c_void_p],
+    "erb_moe_tc_up_act": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                          c_void_p, c_void_p],
     "erb_moe_product": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                         c_int, c_int, c_void_p, c_void_p, c_void_p],
     "erb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -119,7 +129,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
-_LAUNCHES = {"erb_moe_route": 2, "erb_delta_scan": 2, "erb_linear_batched": 0, "erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
+_LAUNCHES = {"erb_diff_part_floats": 0, "erb_moe_route": 2, "erb_delta_scan": 2, "erb_linear_batched": 0, "erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
 SKINNY_MAX_ROWS = 16     # rows up to which the register-fed weight-streaming kernels are used
 TC_MAX_ROWS = 64         # rows up to which the TMA + tcgen05 weight-streaming kernel may be used
 
@@ -202,8 +212,8 @@ def embed_rows(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, sta
 
 def add_rmsnorm(hidden: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
                 delta: torch.Tensor | None = None, rows: torch.Tensor | None = None,
-                write_back: bool = True, settled: bool = False, exact: bool = False) -> None:
-    """out = weight * round(rmsnorm(hidden (+ delta))); hidden += delta in place when write_back.
+                write_back: bool = True, settled: bool = False, exact: bool = False, delta_scale: float = 1.0) -> None:
+    """out = weight * round(rmsnorm(hidden (+ delta_scale * delta))); hidden += delta_scale * delta in place when write_back.
     ``exact``: the normed value stays float until the weight has multiplied it (one rounding, at the store).
     ``delta``: rows of the element type, or float32 partial sums ``[parts, rows, width]`` (what
     ``linear_parts`` leaves) that are added in their order and rounded to the element type once, so that
@@ -225,15 +235,15 @@ def add_rmsnorm(hidden: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, e
     if in_parts:
         _call(_fn("elementwise", _elem(out), "erb_add_rmsnorm_parts"), hidden.data_ptr(), delta.data_ptr(), delta.shape[0],
               delta.stride(0), weight.data_ptr(), out.data_ptr(), _ptr(rows), n, h, float(eps),
-              int(write_back and rows is None), int(bool(settled)) | (2 if exact else 0), _stream())
+              int(write_back and rows is None), int(bool(settled)) | (2 if exact else 0), float(delta_scale), _stream())
         return
     _call(_fn("elementwise", _elem(out), "erb_add_rmsnorm"), hidden.data_ptr(), _ptr(delta), weight.data_ptr(),
           out.data_ptr(), _ptr(rows), n, h, float(eps), int(write_back and rows is None),
-          int(bool(settled)) | (2 if exact else 0), _stream())
+          int(bool(settled)) | (2 if exact else 0), float(delta_scale), _stream())
 
 
-def residual_add(hidden: torch.Tensor, delta: torch.Tensor, dtype: torch.dtype | None = None) -> None:
-    """hidden += delta: rows of the model's element type, or float32 partial sums ``[parts, rows, width]``,
+def residual_add(hidden: torch.Tensor, delta: torch.Tensor, dtype: torch.dtype | None = None, scale: float = 1.0) -> None:
+    """hidden += scale * delta: rows of the model's element type, or float32 partial sums ``[parts, rows, width]``,
     which are added up and rounded to ``dtype`` (the model's element type) once, as ``add_rmsnorm`` does."""
     _need(hidden, "hidden", torch.float32); _need(delta, "delta")
     if delta.dim() == 3:
@@ -241,12 +251,12 @@ def residual_add(hidden: torch.Tensor, delta: torch.Tensor, dtype: torch.dtype |
         if delta.shape[1:] != hidden.shape or dtype is None:
             raise KernelError("residual_add: partial sums need [parts, rows, width] and the element type to round to")
         _call(_fn("elementwise", _ELEM[dtype], "erb_residual_add_parts"), hidden.data_ptr(), delta.data_ptr(), delta.shape[0],
-              delta.stride(0), hidden.numel(), _stream())
+              delta.stride(0), hidden.numel(), float(scale), _stream())
         return
     if hidden.shape != delta.shape:
         raise KernelError("residual_add: shapes disagree")
     _call(_fn("elementwise", _elem(delta), "erb_residual_add"), hidden.data_ptr(), delta.data_ptr(),
-          hidden.numel(), _stream())
+          hidden.numel(), float(scale), _stream())
 
 
 def add_layernorm(hidden: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | None, out: torch.Tensor | None,
@@ -506,6 +516,33 @@ def softcap(logits: torch.Tensor, cap: float, dtype: torch.dtype) -> None:
     n, width = logits.shape
     _call(_fn("elementwise", _ELEM[dtype], "erb_softcap"), logits.data_ptr(), n, width, logits.stride(0) if n > 1 else width,
           float(cap), _stream())
+
+
+ACTS = {"gelu_erf": 0, "relu_squared": 1}
+
+
+def act_rows(x: torch.Tensor, out: torch.Tensor, act: str, gate_col: int = -1) -> None:
+    """out[t, i] = f(x[t, i]) for the first ``out.shape[1]`` columns of the rows ``x`` (a row-strided view allowed), in float,
+    rounded once: ``gelu_erf`` the exact gelu, ``relu_squared`` the square of relu.  ``gate_col >= 0``: every row is also
+    multiplied by the sigmoid of its column ``gate_col`` of ``x`` (one logit per token that scales the whole branch)."""
+    _need(x, "x", contiguous=False); _need(out, "out", x.dtype)
+    n, width = out.shape
+    if x.shape[0] != n or x.shape[1] < width or x.stride(1) != 1 or not -1 <= gate_col < x.shape[1]:
+        raise KernelError("act_rows: shapes disagree")
+    if act not in ACTS:
+        raise KernelError(f"act_rows: unknown activation {act!r}; known: {sorted(ACTS)}")
+    _call(_fn("elementwise", _elem(x), "erb_act_rows"), x.data_ptr(), x.stride(0) if n > 1 else x.shape[1], out.data_ptr(), n, width,
+          ACTS[act], int(gate_col), _stream())
+
+
+def scale_rows(x: torch.Tensor, scale: float, dtype: torch.dtype) -> None:
+    """Float rows times a constant, in place (``x`` may be a view whose rows are further apart than their width)."""
+    _need(x, "x", torch.float32, contiguous=False)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("scale_rows: rows with unit inner stride")
+    n, width = x.shape
+    _call(_fn("elementwise", _ELEM[dtype], "erb_scale_rows"), x.data_ptr(), n, width, x.stride(0) if n > 1 else width, float(scale),
+          _stream())
 
 
 # --- matrix products -------------------------------------------------------------------------
@@ -866,7 +903,7 @@ def latent_scratch_floats(n_tokens: int, n_heads: int, rank: int, n_splits: int)
 def latent_attention(q_lat: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, seq_of_token: torch.Tensor,
                      positions: torch.Tensor, out: torch.Tensor, scale: float, first_token: int, n_tokens: int, *,
                      gate: torch.Tensor | None = None, sink: torch.Tensor | None = None, split_keys: int = 0,
-                     n_splits: int = 1, part: torch.Tensor | None = None) -> None:
+                     n_splits: int = 1, part: torch.Tensor | None = None, window: int = 0) -> None:
     """Causal multi-query attention of tokens ``first_token .. first_token + n_tokens`` over their sequences'
     cache rows ``[c | kr]``: ``q_lat`` float ``[tokens, heads, rank + rot]`` (absorbed and rotated queries),
     ``out[t, h] = gate(t, h) * softmax_j(scale * q_lat[t, h] . row_j (+ sink_h in the denominator)) @ c_j``
@@ -895,7 +932,7 @@ def latent_attention(q_lat: torch.Tensor, pages: torch.Tensor, block_tables: tor
     _call(fn, q_lat.data_ptr(), pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], seq_of_token.data_ptr(),
           positions.data_ptr(), _ptr(gate), 0 if gate is None else (gate.stride(0) if n > 1 else heads), _ptr(sink),
           out.data_ptr(), _ptr(part), int(first_token), int(n_tokens), heads, rank, dk - rank, page_size, int(split_keys),
-          int(n_splits), float(scale), _stream())
+          int(n_splits), float(scale), int(window), _stream())
 
 
 LATENT_MMA_KEYS = 64       # keys per tile of the tensor-core form: splits are multiples of it
@@ -922,11 +959,12 @@ def latent_attention_mma(q_lat: torch.Tensor, pages: torch.Tensor, block_tables:
                          positions: torch.Tensor, out: torch.Tensor, scale: float, first_seq: int, n_seqs: int, first_token: int,
                          n_tokens: int, n_tiles: int, row_tiles: int, *, gate: torch.Tensor | None = None,
                          sink: torch.Tensor | None = None, split_keys: int = 0, n_splits: int = 1,
-                         part: torch.Tensor | None = None) -> None:
+                         part: torch.Tensor | None = None, window: int = 0) -> None:
     """``latent_attention`` on tensor cores for sequences ``first_seq .. first_seq + n_seqs`` of the batch (their
     tokens are rows ``first_token .. first_token + n_tokens``, sequence ``s`` owning ``seq_starts[s] ..
     seq_starts[s + 1]`` and row ``s`` of ``block_tables``).  ``n_tiles = latent_mma_tiles(new tokens per sequence,
-    heads, row_tiles)``; ``split_keys`` a multiple of ``LATENT_MMA_KEYS``."""
+    heads, row_tiles)``; ``split_keys`` a multiple of ``LATENT_MMA_KEYS``.  ``window`` > 0: a query sees its last ``window``
+    keys only; the splits are then counted from the one that holds a row's first visible key."""
     _need(q_lat, "q_lat", torch.float32); _need(pages, "pages", torch.bfloat16); _need(block_tables, "block_tables", torch.int32)
     _need(seq_starts, "seq_starts", torch.int32); _need(positions, "positions", torch.int32)
     _need(out, "out", torch.bfloat16); _need(gate, "gate", torch.bfloat16, contiguous=False); _need(sink, "sink", torch.float32)
@@ -949,10 +987,92 @@ def latent_attention_mma(q_lat: torch.Tensor, pages: torch.Tensor, block_tables:
     _call(_fn("latent_attention", "bfloat16", "erb_latent_attention_mma"), q_lat.data_ptr(), pages.data_ptr(),
           block_tables.data_ptr(), block_tables.shape[1], seq_starts.data_ptr(), positions.data_ptr(), _ptr(gate), gate_ld,
           _ptr(sink), out.data_ptr(), _ptr(part), int(first_token), int(first_seq), int(n_seqs), int(n_tiles), int(row_tiles),
-          heads, rank, dk - rank, pages.shape[2], int(split_keys), int(n_splits), float(scale), _stream())
+          heads, rank, dk - rank, pages.shape[2], int(split_keys), int(n_splits), float(scale), int(window), _stream())
     if n_splits > 1:
         _call(_fn("latent_attention", "bfloat16", "erb_latent_combine"), part.data_ptr(), _ptr(gate), gate_ld, _ptr(sink),
               out.data_ptr(), int(first_token), int(n_tokens), heads, rank, int(n_splits), _stream())
+
+
+# --- differential attention ----------------------------------------------------------------------
+
+DIFF_MAX_V_DIM = 256       # entries of a value row the differential-attention kernel keeps per warp
+
+
+def diff_part_floats(v_dim: int) -> int:
+    """Floats of scratch that one (token, head, split) of ``diff_attention`` takes for value rows of ``v_dim`` entries."""
+    return 4 + 2 * 64 * (1 if v_dim <= 64 else 2 if v_dim <= 128 else 4)
+
+
+def diff_prepare(proj: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int,
+                 v_dim: int, *, inv_freq: torch.Tensor | None = None, rot_dims: int = 0, conv_w: torch.Tensor | None = None,
+                 conv_state: torch.Tensor | None = None, seq_of_token: torch.Tensor | None = None,
+                 seq_starts: torch.Tensor | None = None, state_slots: torch.Tensor | None = None,
+                 slots: torch.Tensor | None = None, k_pages: torch.Tensor | None = None, v_pages: torch.Tensor | None = None,
+                 page_size: int = 1) -> None:
+    """What lies between the fused q/k/v product and a differential attention.  A row of ``proj`` holds ``n_heads``
+    query heads of two maps (``dim`` entries each), ``n_kv_heads`` key heads of two maps and ``n_kv_heads`` value heads
+    (``v_dim``).  ``conv_w`` (float ``[channels, taps]``): a causal convolution over time on every channel, whose inputs
+    before a portion's first token come from the request's record in ``conv_state`` (float ``[slots, taps - 1,
+    channels]``, oldest first); the halves of the first ``rot_dims`` entries of every map of q and k are turned by
+    ``position * inv_freq``; q goes to ``q_out`` ``[tokens, n_heads * 2 * dim]``, k and v to the tokens' cache slots
+    (``k_pages`` ``[pages, kv heads, page_size, 2 * dim]``, ``v_pages`` ``[..., v_dim]``; a negative slot writes nothing)."""
+    _need(proj, "proj", contiguous=False); _need(q_out, "q_out", proj.dtype); _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32); _need(conv_w, "conv_w", torch.float32); _need(conv_state, "conv_state", torch.float32)
+    for name, t in (("seq_of_token", seq_of_token), ("seq_starts", seq_starts), ("state_slots", state_slots), ("slots", slots)):
+        _need(t, name, torch.int32)
+    _need(k_pages, "k_pages", proj.dtype); _need(v_pages, "v_pages", proj.dtype)
+    n = proj.shape[0]
+    channels = (n_heads + n_kv_heads) * 2 * dim + n_kv_heads * v_dim
+    taps = 1 if conv_w is None else conv_w.shape[1]
+    if proj.stride(1) != 1 or proj.shape[1] < channels or q_out.shape != (n, n_heads * 2 * dim) or positions.numel() < n:
+        raise KernelError("diff_prepare: shapes disagree")
+    if rot_dims and (inv_freq is None or inv_freq.numel() != rot_dims // 2):
+        raise KernelError("diff_prepare: inv_freq must hold rot_dims / 2 values")
+    if conv_w is not None and conv_w.shape[0] != channels:
+        raise KernelError("diff_prepare: one row of taps per channel")
+    if taps > 1 and (conv_state is None or tuple(conv_state.shape[1:]) != (taps - 1, channels) or seq_of_token is None
+                     or seq_starts is None or state_slots is None):
+        raise KernelError("diff_prepare: a convolution needs its state [slots, taps - 1, channels] and the step's sequences")
+    if slots is not None:
+        if k_pages is None or v_pages is None or tuple(k_pages.shape[1:]) != (n_kv_heads, page_size, 2 * dim) or \
+                tuple(v_pages.shape[1:]) != (n_kv_heads, page_size, v_dim) or slots.numel() < n:
+            raise KernelError("diff_prepare: pages must be [pages, kv heads, page_size, 2 dim] and [..., v_dim]")
+    _call(_fn("diff_attention", _elem(proj), "erb_diff_prepare"), proj.data_ptr(), n, proj.stride(0) if n > 1 else proj.shape[1],
+          _ptr(conv_w), int(taps), _ptr(conv_state), _ptr(seq_of_token), _ptr(seq_starts), _ptr(state_slots), positions.data_ptr(),
+          _ptr(inv_freq), int(rot_dims), int(n_heads), int(n_kv_heads), int(dim), int(v_dim), q_out.data_ptr(), _ptr(slots),
+          _ptr(k_pages), _ptr(v_pages), int(page_size), _stream())
+
+
+def diff_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
+                   seq_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float,
+                   lam: float, eps: float, out_scale: float, first_token: int, n_tokens: int, *, window: int = 0,
+                   softcap: float = 0.0, split_keys: int = 0, n_splits: int = 1, part: torch.Tensor | None = None) -> None:
+    """Differential attention for rows ``first_token .. first_token + n_tokens`` of the batch: per head two softmax maps
+    over the same values, ``o = map1 - lam * map2``, then ``o * rsqrt(mean(o^2) + eps) * out_scale``.  ``q`` ``[tokens,
+    n_heads * 2 * dim]`` (both maps of a head side by side), ``k_pages`` ``[pages, kv heads, page_size, 2 * dim]``,
+    ``v_pages`` ``[pages, kv heads, page_size, v_dim]``, ``out`` ``[tokens, n_heads * v_dim]``.  Scores are ``q . k *
+    scale``, then ``softcap * tanh(score / softcap)`` where a cap is given; a query sees its last ``window`` keys (0: all).
+    With ``n_splits > 1`` the keys are cut at multiples of ``split_keys``, counted from the split that holds a row's first
+    visible key, and ``part`` takes the splits' states."""
+    _need(q, "q"); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype); _need(out, "out", q.dtype)
+    _need(block_tables, "block_tables", torch.int32); _need(seq_of_token, "seq_of_token", torch.int32)
+    _need(positions, "positions", torch.int32); _need(part, "part", torch.float32)
+    n = q.shape[0]
+    n_kv, page_size, two_dim = k_pages.shape[1:]
+    v_dim = v_pages.shape[3]
+    if two_dim % 2 or q.shape[1] != n_heads * two_dim or out.shape != (n, n_heads * v_dim) or n_heads % n_kv or \
+            tuple(v_pages.shape[1:3]) != (n_kv, page_size) or v_dim > DIFF_MAX_V_DIM:
+        raise KernelError("diff_attention: q, pages and out disagree")
+    if first_token < 0 or first_token + n_tokens > n or seq_of_token.numel() < n or positions.numel() < n:
+        raise KernelError("diff_attention: the token range lies outside the batch")
+    if n_splits > 1 and (part is None or split_keys <= 0 or part.numel() < n_tokens * n_heads * n_splits * diff_part_floats(v_dim)):
+        raise KernelError("diff_attention: the scratch for the splits is too small")
+    fn = _fn("diff_attention", _elem(q), "erb_diff_attention")
+    fn._erb_own = 2 if n_splits > 1 else 1
+    _call(fn, q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
+          seq_of_token.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(part), int(first_token), int(n_tokens), int(n_heads),
+          int(n_kv), two_dim // 2, v_dim, page_size, int(window), int(split_keys), int(n_splits), float(scale), float(softcap),
+          float(lam), float(eps), float(out_scale), _stream())
 
 
 # --- state-space mixer -------------------------------------------------------------------------
@@ -1106,15 +1226,21 @@ def _moe_lists(lists: torch.Tensor, n_tokens: int, n_experts: int, top: int):
     return choice, order, counts, offsets, tiles
 
 
+MOE_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, lists: torch.Tensor, score: torch.Tensor,
-              tile_rows: int = 0) -> None:
+              tile_rows: int = 0, scores: str = "sigmoid", groups: tuple[int, int] | None = None) -> None:
     """Route every row of ``x`` (element type, row-strided view allowed): logits ``w_router x`` in float (``w_router``
     float ``[experts, width]``), the ``top`` largest chosen (the lower index wins a tie), ``score`` float ``[tokens *
     top]`` their sigmoids; ``lists`` (int32, ``moe_lists_ints`` entries) receives the choices and, per expert, the list
     of its (token, choice) pairs in rising order with offsets, all made on the device.  ``tile_rows``: the rows of a tile
     that the lists' tile offsets count (0: those of ``moe_gate_up`` and ``moe_down``; ``moe_tc_tile_rows`` for the
-    tensor-core products)."""
+    tensor-core products).  ``scores``: ``sigmoid`` of the logit, or ``softmax`` over all experts' logits.  ``groups =
+    (count, keep)``: the experts form ``count`` equal groups of neighbours, a group counts as much as its best expert, and
+    only experts of the ``keep`` best groups can be chosen."""
     _need(x, "x", contiguous=False); _need(w_router, "w_router", torch.float32); _need(lists, "lists", torch.int32)
+    n_groups, keep = groups if groups else (1, 1)
     _need(score, "score", torch.float32)
     n, width = x.shape
     n_experts = w_router.shape[0]
@@ -1123,7 +1249,7 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, lists: torch.Te
     choice, order, counts, offsets, tiles = _moe_lists(lists, n, n_experts, top)
     _call(_fn("moe", _elem(x), "erb_moe_route"), x.data_ptr(), x.stride(0) if n > 1 else width, w_router.data_ptr(), n, width,
           n_experts, int(top), choice.data_ptr(), score.data_ptr(), counts.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
-          order.data_ptr(), int(tile_rows), _stream())
+          order.data_ptr(), int(tile_rows), MOE_SCORES[scores], int(n_groups), int(keep), _stream())
 
 
 def moe_tc_supported(dtype: torch.dtype, width: int, ff: int) -> bool:
@@ -1139,14 +1265,15 @@ def moe_tc_tile_rows(n_tokens: int, n_experts: int, top: int) -> int:
     return 16 if share <= 16 else 32 if share <= 32 else 64 if share <= 64 else 128
 
 
-def moe_tc_gather(x: torch.Tensor, lists: torch.Tensor, score: torch.Tensor, n_experts: int, top: int, xs: torch.Tensor) -> None:
-    """xs[list row] = round(score * x[token]) for every (token, choice) pair, in the order of the experts' lists."""
+def moe_tc_gather(x: torch.Tensor, lists: torch.Tensor, score: torch.Tensor | None, n_experts: int, top: int, xs: torch.Tensor) -> None:
+    """xs[list row] = round(score * x[token]) for every (token, choice) pair, in the order of the experts' lists
+    (``score`` None: the rows as they are)."""
     _need(x, "x", torch.bfloat16, contiguous=False); _need(xs, "xs", torch.bfloat16); _need(score, "score", torch.float32)
     n, width = x.shape
     if xs.shape != (n * top, width) or x.stride(1) != 1:
         raise KernelError("moe_tc_gather: shapes disagree")
     _, order, _, _, _ = _moe_lists(lists, n, n_experts, top)
-    _call(_fn("moe_tc", None, "erb_moe_tc_gather"), x.data_ptr(), x.stride(0) if n > 1 else width, order.data_ptr(), score.data_ptr(),
+    _call(_fn("moe_tc", None, "erb_moe_tc_gather"), x.data_ptr(), x.stride(0) if n > 1 else width, order.data_ptr(), _ptr(score),
           int(top), n, width, xs.data_ptr(), _stream())
 
 
@@ -1164,16 +1291,32 @@ def moe_tc_gate_up(xs: torch.Tensor, w_gate_up: torch.Tensor, lists: torch.Tenso
           _stream())
 
 
-def moe_tc_down(act: torch.Tensor, w_down: torch.Tensor, lists: torch.Tensor, top: int, tile_rows: int, parts: torch.Tensor) -> None:
+def moe_tc_up_act(xs: torch.Tensor, w_up: torch.Tensor, lists: torch.Tensor, top: int, tile_rows: int, act: torch.Tensor) -> None:
+    """``moe_up_act`` on tensor cores, from the gathered rows ``xs``: act[list row] = relu(W_up r)^2; ``w_up`` ``[experts, ff, width]``."""
+    _need(xs, "xs", torch.bfloat16); _need(w_up, "w_up", torch.bfloat16); _need(act, "act", torch.bfloat16)
+    pairs, width = xs.shape
+    n_experts, ff, k = w_up.shape
+    if k != width or pairs % top or act.shape != (pairs, ff):
+        raise KernelError("moe_tc_up_act: shapes disagree")
+    _, order, _, offsets, tiles = _moe_lists(lists, pairs // top, n_experts, top)
+    _call(_fn("moe_tc", None, "erb_moe_tc_up_act"), xs.data_ptr(), w_up.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
+          order.data_ptr(), n_experts, int(top), pairs // top, ff, width, int(tile_rows), act.data_ptr(), _ptr(_status_word),
+          _stream())
+
+
+def moe_tc_down(act: torch.Tensor, w_down: torch.Tensor, lists: torch.Tensor, top: int, tile_rows: int, parts: torch.Tensor,
+                out_score: torch.Tensor | None = None) -> None:
     """``moe_down`` on tensor cores; the lists must have been made with ``tile_rows`` rows a tile."""
     _need(act, "act", torch.bfloat16); _need(w_down, "w_down", torch.bfloat16); _need(parts, "parts", torch.float32)
+    _need(out_score, "out_score", torch.float32)
     n_experts, width, ff = w_down.shape
     n = act.shape[0] // top
     if act.shape != (n * top, ff) or parts.dim() != 3 or parts.shape[0] < top or parts.shape[1:] != (n, width):
         raise KernelError("moe_tc_down: shapes disagree")
     _, order, _, offsets, tiles = _moe_lists(lists, n, n_experts, top)
     _call(_fn("moe_tc", None, "erb_moe_tc_down"), act.data_ptr(), w_down.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
-          order.data_ptr(), n_experts, int(top), n, width, ff, int(tile_rows), parts.data_ptr(), _ptr(_status_word), _stream())
+          order.data_ptr(), n_experts, int(top), n, width, ff, int(tile_rows), parts.data_ptr(), _ptr(out_score), _ptr(_status_word),
+          _stream())
 
 
 def moe_gate_up(x: torch.Tensor, w_gate_up: torch.Tensor, lists: torch.Tensor, score: torch.Tensor, top: int,
@@ -1191,17 +1334,33 @@ def moe_gate_up(x: torch.Tensor, w_gate_up: torch.Tensor, lists: torch.Tensor, s
           1, act.data_ptr(), None, _stream())
 
 
-def moe_down(act: torch.Tensor, w_down: torch.Tensor, lists: torch.Tensor, top: int, parts: torch.Tensor) -> None:
+def moe_up_act(x: torch.Tensor, w_up: torch.Tensor, lists: torch.Tensor, top: int, act: torch.Tensor) -> None:
+    """act[list row] = relu(W_up x[token])^2 for every (token, choice) pair, in the order of the experts' lists: experts
+    without a gate branch.  ``w_up`` ``[experts, ff, width]``."""
+    _need(x, "x", contiguous=False); _need(w_up, "w_up", x.dtype); _need(act, "act", x.dtype)
+    n, width = x.shape
+    n_experts, ff, k = w_up.shape
+    if k != width or act.shape != (n * top, ff) or x.stride(1) != 1:
+        raise KernelError("moe_up_act: shapes disagree")
+    _, order, _, offsets, tiles = _moe_lists(lists, n, n_experts, top)
+    _call(_fn("moe", _elem(x), "erb_moe_product"), x.data_ptr(), x.stride(0) if n > 1 else width, w_up.data_ptr(),
+          offsets.data_ptr(), tiles.data_ptr(), order.data_ptr(), None, n_experts, int(top), n, ff, width,
+          2, act.data_ptr(), None, _stream())
+
+
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, lists: torch.Tensor, top: int, parts: torch.Tensor,
+             out_score: torch.Tensor | None = None) -> None:
     """parts[choice, token] = W_down[expert] act[list row]: float ``[>= top, tokens, width]`` partial sums of the
-    tokens' updates, one per choice.  ``w_down`` ``[experts, width, ff]``."""
+    tokens' updates, one per choice (times the pair's ``out_score`` where given).  ``w_down`` ``[experts, width, ff]``."""
     _need(act, "act"); _need(w_down, "w_down", act.dtype); _need(parts, "parts", torch.float32)
+    _need(out_score, "out_score", torch.float32)
     n_experts, width, ff = w_down.shape
     n = act.shape[0] // top
     if act.shape != (n * top, ff) or parts.dim() != 3 or parts.shape[0] < top or parts.shape[1:] != (n, width):
         raise KernelError("moe_down: shapes disagree")
     _, order, _, offsets, tiles = _moe_lists(lists, n, n_experts, top)
     _call(_fn("moe", _elem(act), "erb_moe_product"), act.data_ptr(), ff, w_down.data_ptr(), offsets.data_ptr(),
-          tiles.data_ptr(), order.data_ptr(), None, n_experts, int(top), n, width, ff, 0, None, parts.data_ptr(), _stream())
+          tiles.data_ptr(), order.data_ptr(), _ptr(out_score), n_experts, int(top), n, width, ff, 0, None, parts.data_ptr(), _stream())
 
 
 # --- attention -------------------------------------------------------------------------------

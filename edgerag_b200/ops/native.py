@@ -32,6 +32,7 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...], bool]] = {
     "elementwise": ("elementwise.cu", (), True),
     "attention": ("attention.cu", (), True),
     "latent_attention": ("latent_attention.cu", (), True),
+    "diff_attention": ("diff_attention.cu", (), True),
     "ssm": ("ssm.cu", (), True),
     "delta": ("delta.cu", (), True),
     "moe": ("moe.cu", (), True),

@@ -17,7 +17,8 @@ Interfaces (duck-typed; the base classes document them):
 * ``Mixer.cache_spec()`` and ``Mixer.forward(x, ctx, call) -> Tensor``;
 * ``FeedForward.forward(x, ctx) -> Tensor``;
 * ``Block.forward(hidden, delta, ctx, call) -> delta`` (the update that is still to be added: rows, float32
-  partial sums, or a ``NormedUpdate`` when a norm has to act on it before the add);
+  partial sums, a ``NormedUpdate`` when a norm has to act on it before the add, or a ``ScaledUpdate`` when a
+  constant multiplies it);
 * ``StreamOp.begin(ctx, hidden)`` and ``StreamOp.forward(hidden, delta, ctx, call) -> delta``: a step of the run
   order between layers that rewrites the residual stream itself (``StreamCall`` in the plan's schedule).
 """
@@ -104,6 +105,16 @@ class NormedUpdate:
     norm: "Norm"
     #: a float vector added to every row of ``tensor`` before the norm acts (a projection's bias that rides along)
     bias: "torch.Tensor | None" = None
+
+
+@dataclass
+class ScaledUpdate:
+    """An update of the residual stream that a constant multiplies as it is added: ``hidden += scale * tensor``
+    (``tensor``: rows or float32 partial sums).  A block whose model scales every sublayer's output hands this on as its
+    ``delta``; the multiplication happens in float inside whatever kernel adds the update."""
+
+    tensor: torch.Tensor
+    scale: float
 
 
 @dataclass
@@ -229,6 +240,8 @@ def settle_update(hidden: torch.Tensor, delta: "torch.Tensor | NormedUpdate | No
             delta.norm.add_normed(hidden, delta.tensor, bias=delta.bias)
         else:
             delta.norm.add_normed(hidden, delta.tensor)
+    elif isinstance(delta, ScaledUpdate):
+        kernels.residual_add(hidden, delta.tensor, dtype, scale=delta.scale)
     else:
         kernels.residual_add(hidden, delta, dtype)
 

@@ -17,7 +17,8 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
-from .base import Block, FeedForward, LayerCall, Mixer, Norm, NormedUpdate, PartSpec, WeightSpec, build_part, register_part
+from .base import (Block, FeedForward, LayerCall, Mixer, Norm, NormedUpdate, PartSpec, ScaledUpdate, WeightSpec, build_part,
+                   register_part)
 
 
 @register_part("block", "prenorm")
@@ -25,8 +26,10 @@ class PreNormBlock(Block):
     graph_safe = True
 
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm | None, ffn: FeedForward | None, hidden: int,
-                 dtype: torch.dtype, device: torch.device) -> None:
-        """``norm2`` and ``ffn`` are None for a layer that is its mixer's sublayer only."""
+                 dtype: torch.dtype, device: torch.device, update_scale: float = 1.0) -> None:
+        """``norm2`` and ``ffn`` are None for a layer that is its mixer's sublayer only.  ``update_scale`` m:
+        ``h += m * mixer(norm1(h)); h += m * ffn(norm2(h))`` (the norms then have to take a ``ScaledUpdate``)."""
+        self.update_scale = float(update_scale)
         if getattr(mixer, "has_update_bias", False):
             raise ValueError("a mixer whose update carries a bias needs a block that closes the update with a norm")
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
@@ -43,12 +46,13 @@ class PreNormBlock(Block):
         self.norm1.forward(hidden, x, delta, settled=settled())   # hidden += delta; x = norm1(hidden)
         if delta is not None:
             ctx.stream_written = kernels.launches()
-        mixed = self.mixer.forward(x, ctx, call)
+        scaled = (lambda u: ScaledUpdate(u, self.update_scale)) if self.update_scale != 1.0 else (lambda u: u)   # noqa: E731
+        mixed = scaled(self.mixer.forward(x, ctx, call))
         if self.ffn is None:
             return mixed                               # added by whichever norm comes next
         self.norm2.forward(hidden, x, mixed, settled=settled())   # hidden += mixed; x = norm2(hidden)
         ctx.stream_written = kernels.launches()
-        return self.ffn.forward(x, ctx)               # added by whichever norm comes next
+        return scaled(self.ffn.forward(x, ctx))       # added by whichever norm comes next
 
 
 @register_part("block", "sandwich")

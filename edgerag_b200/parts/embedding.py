@@ -56,10 +56,12 @@ class LMHead(Part):
     graph_safe = True
 
     def __init__(self, vocab: int, hidden: int, dtype: torch.dtype, device: torch.device,
-                 tied_to: str | None = None, softcap: float = 0.0, tensor: str = "weight") -> None:
+                 tied_to: str | None = None, softcap: float = 0.0, tensor: str = "weight", scale: float = 1.0) -> None:
         """``tied_to``: model-relative name of the tensor to share when the checkpoint has no head of
         its own (the plan names it; this part does not know what the model calls its embedding).
-        ``softcap`` c > 0: logits <- c * tanh(logits / c), in float."""
+        ``softcap`` c > 0: logits <- c * tanh(logits / c), in float; ``scale``: a constant that multiplies the
+        float logits (after the cap)."""
+        self.scale = float(scale)
         self.vocab, self.hidden, self.tied_to = vocab, hidden, tied_to
         self.dtype, self.device = dtype, device
         self.softcap, self.tensor = float(softcap or 0.0), tensor
@@ -75,3 +77,5 @@ class LMHead(Part):
         kernels.linear(x, self.weight, logits)
         if self.softcap > 0.0:
             kernels.softcap(logits, self.softcap, self.dtype)
+        if self.scale != 1.0:
+            kernels.scale_rows(logits, self.scale, self.dtype)

@@ -13,6 +13,8 @@ attention kernel is multi-query attention over the cache rows, shared by all hea
 have a sink per head (a learnt logit that takes part in the denominator only), the queries may come
 through a normed latent of their own (``q_rank``), and a layer may read the cache rows that another
 layer wrote (``own_kv=False`` with a ``LayerCall`` that names that layer's cache and does not write).
+With ``window`` a query sees its last ``window`` cache rows only (itself among them), the pages behind the
+window go back to the pool, and ``gated=False`` leaves the sigmoid gate out.
 
 The first product reads the mixer's input once for everything that is made from it: queries (or
 their latent), the down-projection of ``[c | kr]`` and the gate logits.
@@ -25,6 +27,7 @@ import torch
 from ..cache.manager import KVGroupSpec
 from ..ops import kernels
 from .base import LayerCall, Mixer, WeightSpec, register_part
+from .rope import rotary_frequencies
 
 
 def _pad8(n: int) -> int:
@@ -37,13 +40,17 @@ class LatentAttention(Mixer):
 
     def __init__(self, hidden: int, n_heads: int, dim: int, rot_dim: int, v_dim: int, kv_rank: int, scale: float,
                  rot_base: float, rot_dims: int, eps: float, dtype: torch.dtype, device: torch.device, q_rank: int = 0,
-                 sink: bool = False, own_kv: bool = True, gated: bool = True) -> None:
+                 sink: bool = False, own_kv: bool = True, gated: bool = True, window: int = 0,
+                 rot_scaling: dict | None = None) -> None:
         if rot_dim % 2 or rot_dims % 2 or rot_dims > rot_dim or kv_rank % 2:
             raise ValueError("latent attention: kv_rank, rot_dim and the rotated dimensions must be even, rot_dims <= rot_dim")
         self.hidden, self.n_heads, self.dim, self.rot_dim, self.v_dim = hidden, n_heads, dim, rot_dim, v_dim
         self.kv_rank, self.q_rank, self.rot_dims = kv_rank, int(q_rank or 0), rot_dims
         self.scale, self.eps = float(scale), float(eps)
         self.sink_on, self.own_kv, self.gated = bool(sink), bool(own_kv), bool(gated)
+        self.window = int(window or 0)
+        if self.window < 0:
+            raise ValueError("latent attention: a window is positive (or 0 for none)")
         self.dtype, self.device = dtype, device
         self.q_width = n_heads * (dim + rot_dim)
         # columns of the fused first product: [queries or their latent | c and kr before norm and turn | gate logits]
@@ -51,13 +58,12 @@ class LatentAttention(Mixer):
         self.off_kv = first
         self.off_g = first + (kv_rank + rot_dim if own_kv else 0)
         self.in_width = _pad8(self.off_g + (n_heads if gated else 0))
-        i = torch.arange(rot_dims // 2, dtype=torch.float64)
-        self.inv_freq = (float(rot_base) ** (-2.0 * i / max(rot_dims, 1))).to(device=device, dtype=torch.float32).contiguous()
+        self.inv_freq = rotary_frequencies(rot_base, rot_dims, rot_scaling).to(device=device, dtype=torch.float32).contiguous()
         self.w_in = self.w_uq = self.w_uk_t = self.w_uv = self.w_o = None
         self.kv_norm = self.q_norm = self.sink = None
 
     def cache_spec(self) -> KVGroupSpec:
-        return KVGroupSpec(1, 1, self.kv_rank + self.rot_dim, 0, v_head_dim=0)
+        return KVGroupSpec(1, 1, self.kv_rank + self.rot_dim, self.window, v_head_dim=0)
 
     def weight_specs(self) -> list[WeightSpec]:
         H, r = self.n_heads, self.kv_rank
@@ -103,9 +109,13 @@ class LatentAttention(Mixer):
         """(keys per split, splits) for the single-token rows: enough blocks for ``waves`` blocks per SM, splits
         of a multiple of 64 keys at multiples of their size; a function of the row count and the context bound alone."""
         bound = max(1, ctx.max_keys_bound())
-        want = max(1, min(-(-waves * kernels._sms(self.device) // max(1, n_blocks)), -(-bound // 64), kernels.LATENT_MAX_SPLITS))
-        split = -(-(-(-bound // want)) // 64) * 64
-        return split, -(-bound // split)
+        reach = min(bound, self.window) if self.window else bound        # keys a row reads
+        want = max(1, min(-(-waves * kernels._sms(self.device) // max(1, n_blocks)), -(-reach // 64), kernels.LATENT_MAX_SPLITS))
+        split = -(-(-(-reach // want)) // 64) * 64
+        n_splits = -(-bound // split)
+        if self.window:     # a window of w keys touches at most (w - 1) // split + 2 splits, wherever it lies
+            n_splits = min(n_splits, (self.window - 1) // split + 2)
+        return split, n_splits
 
     def _attend(self, ctx, q_lat, pages, tables, o_lat, gate) -> None:
         n, H, r = q_lat.shape[0], self.n_heads, self.kv_rank
@@ -118,20 +128,21 @@ class LatentAttention(Mixer):
                 split, n_splits = self._decode_plan(ctx, tiles, 1)
                 part = ctx.buf("latent.part", (kernels.latent_scratch_floats(nd, H, r, n_splits),), torch.float32) if n_splits > 1 else None
                 kernels.latent_attention_mma(q_lat, pages, tables, ctx.seq_starts, ctx.positions, o_lat, self.scale, 0, nd, 0, nd,
-                                             tiles, mt, gate=gate, sink=self.sink, split_keys=split, n_splits=n_splits, part=part)
+                                             tiles, mt, gate=gate, sink=self.sink, split_keys=split, n_splits=n_splits, part=part,
+                                             window=self.window)
             if n > nd:
                 tiles = kernels.latent_mma_tiles(ctx.host_q_len[nd:], H, 2)
                 kernels.latent_attention_mma(q_lat, pages, tables, ctx.seq_starts, ctx.positions, o_lat, self.scale, nd,
-                                             ctx.n_seqs - nd, nd, n - nd, tiles, 2, gate=gate, sink=self.sink)
+                                             ctx.n_seqs - nd, nd, n - nd, tiles, 2, gate=gate, sink=self.sink, window=self.window)
             return
         if nd:
             split, n_splits = self._decode_plan(ctx, -(-nd * H // 4), 2)
             part = ctx.buf("latent.part", (kernels.latent_scratch_floats(nd, H, r, n_splits),), torch.float32) if n_splits > 1 else None
             kernels.latent_attention(q_lat, pages, tables, ctx.seq_of_token, ctx.positions, o_lat, self.scale, 0, nd,
-                                     gate=gate, sink=self.sink, split_keys=split, n_splits=n_splits, part=part)
+                                     gate=gate, sink=self.sink, split_keys=split, n_splits=n_splits, part=part, window=self.window)
         if n > nd:
             kernels.latent_attention(q_lat, pages, tables, ctx.seq_of_token, ctx.positions, o_lat, self.scale, nd, n - nd,
-                                     gate=gate, sink=self.sink)
+                                     gate=gate, sink=self.sink, window=self.window)
 
     def forward(self, x: torch.Tensor, ctx, call: LayerCall) -> torch.Tensor:
         n, H, r, dr = x.shape[0], self.n_heads, self.kv_rank, self.rot_dim

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
-from .base import Norm, NormedUpdate, WeightSpec, register_part, settle_update
+from .base import Norm, NormedUpdate, ScaledUpdate, WeightSpec, register_part, settle_update
 
 
 @register_part("norm", "rmsnorm")
@@ -51,8 +51,11 @@ class RMSNorm(Norm):
                 raise ValueError("a pending update that another kind of norm has to close can only be added to all rows")
             settle_update(hidden, delta, self.dtype)
             delta, settled = None, False
+        scale = 1.0
+        if isinstance(delta, ScaledUpdate):      # the constant rides into the kernel that adds the update
+            delta, scale = delta.tensor, delta.scale
         kernels.add_rmsnorm(hidden, self.weight, out, self.eps, delta=delta, rows=rows, write_back=write_back, settled=settled,
-                            exact=self.exact)
+                            exact=self.exact, delta_scale=scale)
 
     def add_normed(self, hidden: torch.Tensor, x: torch.Tensor, bias: torch.Tensor | None = None) -> None:
         kernels.rms_between(hidden, None, delta=x, bias=bias, post=(self._plain_weight(), self.eps), dtype=self.dtype)

@@ -16,10 +16,30 @@ part has already put positions into the stream.
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..ops import kernels
 from .base import PositionEncoding, register_part
+
+
+def rotary_frequencies(base: float, dims: int, scaling: dict | None = None) -> torch.Tensor:
+    """``f_i = base^(-2i / dims)`` for ``i < dims / 2``, made in float64.  ``scaling = {factor, low, high, original}``
+    stretches the long wavelengths: with ``l = 2 pi / f``, a frequency stays where ``l < original / high``, becomes
+    ``f / factor`` where ``l > original / low``, and in between is the blend ``(1 - s) f / factor + s f`` with
+    ``s = (original / l - low) / (high - low)``."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / max(dims, 1))
+    if scaling:
+        factor, low, high, original = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+        if not (factor > 0 and high > low and original > 0):
+            raise ValueError("rotary scaling needs factor > 0, high > low and original > 0")
+        wavelength = 2.0 * math.pi / f
+        s = ((original / wavelength - low) / (high - low)).clamp(0.0, 1.0)
+        blend = (1.0 - s) * f / factor + s * f
+        f = torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, blend))
+    return f
 
 
 @register_part("position", "rope_halves")
