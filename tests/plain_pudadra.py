@@ -180,8 +180,12 @@ def routed_choice(h: torch.Tensor, w_router: torch.Tensor, router: dict) -> tupl
     return chosen, s.gather(1, chosen)
 
 
-def moe_ff(h: torch.Tensor, w: dict, pre: str, mlp: dict) -> torch.Tensor:
-    chosen, weight = routed_choice(h, w[pre + "router"], mlp["router"])
+def moe_ff(h: torch.Tensor, w: dict, pre: str, mlp: dict, chosen: torch.Tensor | None = None) -> torch.Tensor:
+    """``chosen`` [T, top]: experts handed in (their weights are still this router's scores), else the router's own."""
+    if chosen is None:
+        chosen, weight = routed_choice(h, w[pre + "router"], mlp["router"])
+    else:
+        weight = torch.softmax(h @ w[pre + "router"].to(F64).T, -1).gather(1, chosen.long())
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(chosen[t].tolist(), weight[t].tolist()):
@@ -192,8 +196,9 @@ def moe_ff(h: torch.Tensor, w: dict, pre: str, mlp: dict) -> torch.Tensor:
     return out
 
 
-def forward(w: dict, cfg: dict, tokens: list[int], layers_out: list | None = None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence; ``layers_out`` receives the stream after every layer."""
+def forward(w: dict, cfg: dict, tokens: list[int], layers_out: list | None = None, chosen: dict | None = None) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence; ``layers_out`` receives the stream after every layer; ``chosen``: layer -> the
+    experts [T, top] to use there instead of the router's choice."""
     eps, mult = cfg["norm"]["eps"], cfg["residual_mult"]
     x = w["embed"].to(F64)[torch.tensor(tokens)]
     for i, layer in enumerate(cfg["layers"]):
@@ -204,7 +209,10 @@ def forward(w: dict, cfg: dict, tokens: list[int], layers_out: list | None = Non
         mlp = layer.get("mlp")
         if mlp:
             h = layer_norm_w(x, w[pre + "norm2"].to(F64), eps)
-            ff = dense_ff(h, w, pre + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, w, pre + "mlp.", mlp)
+            if mlp["kind"] == "dense":
+                ff = dense_ff(h, w, pre + "mlp.")
+            else:
+                ff = moe_ff(h, w, pre + "mlp.", mlp, None if chosen is None else chosen.get(i))
             x = x + mult * ff
         if layers_out is not None:
             layers_out.append(x.clone())
