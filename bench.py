@@ -581,6 +581,29 @@ def lozanex_config(size: dict, n_layers: int) -> dict:
     return {"architecture": "Lozanex", "width": size["width"], "vocab": size["vocab"], "norm": {"eps": 1e-5}, "layers": layers}
 
 
+#: the Pudadra sizes beside DESIGN_SIZES: differential heads of two maps of 64 with values of 128 (a quarter as many kv
+#: heads), windows of 1,024 for both mixers, and routed experts sized as Lozanex's (top * ff / 8 + ff / 2 per token)
+PUDADRA_WINDOW = 1024
+PUDADRA_ROUTER = {"experts": 32, "top": 4, "groups": {"count": 8, "keep": 4}}
+
+
+def pudadra_config(size: dict, n_layers: int) -> dict:
+    """Layers in the order differential attention, differential attention, latent attention, repeated; the first layer
+    with a dense feed-forward, the others with routed experts and a shared expert."""
+    heads = size["width"] // 128
+    diff = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.6, "softcap": 30.0,
+            "conv": 4, "mask": {"size": PUDADRA_WINDOW},
+            "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    att = {k: v for k, v in size["att"].items() if k != "q_rank"}
+    latent = dict(att, scale=(att["dim"] + att["rot_dim"]) ** -0.5, rot={"base": 1000000.0, "dims": att["rot_dim"]},
+                  mask={"size": PUDADRA_WINDOW})
+    moe = {"kind": "moe", "expert": {"ff": size["ff"] // 8}, "router": dict(PUDADRA_ROUTER), "shared": {"ff": size["ff"] // 2}}
+    layers = [{"type": "latent_attention" if i % 3 == 2 else "attention", "mixer": dict(latent if i % 3 == 2 else diff),
+               "mlp": {"kind": "dense", "ff": size["ff"]} if i == 0 else moe} for i in range(n_layers)]
+    return {"architecture": "Pudadra", "width": size["width"], "vocab": size["vocab"], "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "logit_scale": 1.0, "layers": layers}
+
+
 def run_designs(args) -> dict:
     """Prefill (one portion of 2,048 tokens) and decode (batch 1 and --batch at a context of 2,048) of one design
     (--design) and of the Llama decoder at the same width, feed-forward size, vocabulary and number of layer
@@ -658,6 +681,8 @@ def run_designs(args) -> dict:
         return run_vokusun(args, measure, n_layers, block, clocks, peak_source, microbench)
     if args.design == "lozanex":
         return run_lozanex(args, measure, n_layers, block, clocks, peak_source, microbench)
+    if args.design == "pudadra":
+        return run_pudadra(args, measure, n_layers, block, clocks, peak_source, microbench)
     for name, size in DESIGN_SIZES.items():
         out[name] = {"layers": n_layers, "dokodra": measure(dokodra_config(size, n_layers), size["vocab"]),
                      "llama": measure(llama_config(size, n_layers), size["vocab"])}
@@ -799,6 +824,64 @@ def run_lozanex(args, measure, n_layers: int, block: int, clocks, peak_source: s
             "sizes": out, "kernels": kern, "step_kernels": steps, "clocks": clocks.record()}
 
 
+def run_pudadra(args, measure, n_layers: int, block: int, clocks, peak_source: str, microbench) -> dict:
+    """Pudadra beside Vokusun (the framework's other design of windowed and latent attention) at equal width, layer runs
+    and feed-forward width per token, then its kernels beside the like kernels of Vokusun and Lozanex at equal work,
+    then which kernels a step of each spends its time in."""
+    import subprocess
+    import tempfile
+    import types
+
+    out: dict = {}
+    for name, size in DESIGN_SIZES.items():
+        out[name] = {"layers": n_layers, "pudadra": measure(pudadra_config(size, n_layers), size["vocab"]),
+                     "vokusun": measure(vokusun_config(size, min(n_layers, 4)), size["vocab"])}
+    size = DESIGN_SIZES["w2048"]
+    att, win = size["att"], PUDADRA_WINDOW
+    ns = lambda **kw: types.SimpleNamespace(dtype="bfloat16", iters=10, warmup=3, page=block, sequential_pages=False, **kw)  # noqa: E731
+    heads = dict(heads=32, kv_heads=8, head_dim=64)
+    diff = dict(heads=16, kv_heads=4, dim=64, vdim=128, window=win, softcap=30.0, split=0)
+    lat = dict(heads=att["heads"], rank=att["kv_rank"], rot=att["rot_dim"], split=0, kernel="mma")
+    moe = dict(width=size["width"], ff=size["ff"] // 8, experts=PUDADRA_ROUTER["experts"], top=PUDADRA_ROUTER["top"])
+    pre = lambda tokens, **kw: microbench.prefill_attention(ns(tokens=tokens, past=0, kernel="tc", key_splits=0, **heads, **kw))  # noqa: E731
+    dec = lambda **kw: microbench.decode_attention(ns(batch=64, split=0, head_group=0, cold=True, **heads, **kw))  # noqa: E731
+    kern = {
+        "diff_attention_prefill_2048": microbench.diff_attention(ns(batch=1, context=0, tokens=2048, past=0, cold=False, **diff)),
+        "diff_attention_prefill_8192": microbench.diff_attention(ns(batch=1, context=0, tokens=8192, past=0, cold=False, **diff)),
+        "window_attention_prefill_2048": pre(2048, window=win, keep_first=0),
+        "window_attention_prefill_8192": pre(8192, window=win, keep_first=0),
+        "diff_attention_decode_b64_ctx8192": microbench.diff_attention(ns(batch=64, context=8192, tokens=0, past=0, cold=True, **diff)),
+        "diff_attention_decode_b8_ctx8192": microbench.diff_attention(ns(batch=8, context=8192, tokens=0, past=0, cold=True, **diff)),
+        "window_attention_decode_b64_ctx8192_gqa": dec(context=8192, kernel="gqa", window=win, keep_first=0),
+        "window_attention_decode_b64_ctx8192_bulk": dec(context=8192, kernel="bulk", window=win, keep_first=0),
+        "latent_window_decode_b8_ctx8192": microbench.latent_attention(ns(batch=8, context=8192, tokens=0, past=0, cold=True, window=win, **lat)),
+        "latent_decode_b8_ctx1024": microbench.latent_attention(ns(batch=8, context=1024, tokens=0, past=0, cold=True, **lat)),
+        "latent_window_prefill_8192": microbench.latent_attention(ns(batch=1, context=0, tokens=8192, past=0, cold=False, window=win, **lat)),
+        "latent_prefill_2048": microbench.latent_attention(ns(batch=1, context=0, tokens=2048, past=0, cold=False, **lat)),
+    }
+    for rows in (8, 64, 2048):
+        kern[f"ungated_experts_{rows}_rows"] = microbench.routed_experts(ns(tokens=rows, ungated=True, groups=(8, 4), **moe))
+        kern[f"gated_experts_{rows}_rows"] = microbench.routed_experts(ns(tokens=rows, **moe))
+    steps = {}
+    for name, cfg in (("pudadra", pudadra_config(size, 3)), ("vokusun", vokusun_config(size, 3))):
+        with tempfile.NamedTemporaryFile("w", suffix=".json") as f:
+            json.dump(cfg, f)
+            f.flush()
+            done = subprocess.run([sys.executable, "-m", "edgerag_b200.ops.microbench", "step-kernels", "--config-json", f.name,
+                                   "--batch", str(args.batch), "--context", "2048", "--tokens", "2048", "--iters", "4", "--rows", "16"],
+                                  cwd=str(ROOT), env=dict(os.environ, EDGERAG_B200_NO_CHAIN="1"), capture_output=True, text=True)
+        if done.returncode != 0:
+            raise RuntimeError(f"step-kernels of {name} failed: {done.stderr[-400:]}")
+        steps[name] = json.loads(done.stdout.strip().splitlines()[-1])
+    return {"metric": "design_compare", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "dtype": "bf16",
+            "data": "synthetic", "impl": "ours", "higher_is_better": True,
+            "config": {"designs": ["Pudadra", "Vokusun"], "prefill_tokens": 2048, "decode_context": 2048,
+                       "decode_batches": sorted({1, args.batch}), "page_tokens": block, "window": PUDADRA_WINDOW,
+                       "routed_experts": PUDADRA_ROUTER, "peaks": peak_source,
+                       "l2": "decode: weights and cache larger than L2 at w2048; kernels: caches and weights rotated (cold)"},
+            "sizes": out, "kernels": kern, "step_kernels": steps, "clocks": clocks.record()}
+
+
 def _tensors_of(model) -> list:
     import torch
 
@@ -826,7 +909,7 @@ def main() -> int:
                     help="decode: the headline measurement; mixed / continuous: the serving workloads of the "
                          "256M and 500M decoders through Engine.generate; designs: prefill and decode of one design "
                          "(--design) beside the Llama decoder at equal sizes, and its kernels against their rooflines")
-    ap.add_argument("--design", choices=["dokodra", "vokusun", "lozanex"], default="dokodra",
+    ap.add_argument("--design", choices=["dokodra", "vokusun", "lozanex", "pudadra"], default="dokodra",
                     help="with --workload designs: the design that is measured beside the Llama decoder")
     ap.add_argument("--ref-cpu-check", action="store_true",
                     help="with --impl reference: a dry run of the reference arm's loop at toy sizes on the CPU")

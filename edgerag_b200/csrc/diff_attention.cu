@@ -18,6 +18,8 @@
 // at offset p % page_size.  Query head h reads kv head h / (H / G).  A query at position p sees the keys
 // first_visible_key(p, window) .. p.  Splits lie at multiples of `split_keys`, counted from the one that holds the
 // first visible key, so a token's sums do not depend on what else is in the step.
+#include <algorithm>
+
 #include "common.cuh"
 
 using namespace erb;
@@ -306,6 +308,419 @@ diff_combine_kernel(const float* __restrict__ part, T* __restrict__ out, int fir
   store_head<T, VI>(out + ((size_t)t * H + h) * vdim, a1, vdim);
 }
 
+#if ERB_ELEM == 1
+// ---------------------------------------------------------------------------------------------
+// The same attention on tensor cores (bfloat16).  A block owns 64 neighbouring rows of one sequence and one kv head, a
+// row being a (token, query head of that kv head) pair with the heads running fastest: the heads of a group meet their
+// keys and values once.  Warp w owns 16 of the rows.  A portion of a prompt fills the tiles; a single token brings H / G
+// rows, and its keys may be cut into splits (grid z) whose states a second kernel merges.  Keys and values arrive in tiles of 64 keys by 16-byte asynchronous
+// copies straight from the pages into one of two stages of shared memory (rows past the end are filled with zeros).  Per
+// tile and map: S = Q_m K_m^T by mma.sync m16n8k16 (queries and keys by ldmatrix, float accumulation), then scale, cap and
+// mask in float, the running maximum and the weights exp(s - max) per row in float, the weights rounded to bfloat16 as
+// the A operand of  O_m += P_m V  (values by ldmatrix.trans from the same stage: both maps read one value tile).  The
+// epilogue is that of the general kernel, per row inside a quad of lanes.
+// VT: pairs of 8-column tiles of the value row a warp accumulates (vdim <= 16 VT).
+// ---------------------------------------------------------------------------------------------
+constexpr int kMmaRows = 64, kMmaKeys = 64, kMmaWarps = 4;
+
+__device__ __forceinline__ void ldsm4(uint32_t* r, const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t* r, const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void copy16(void* dst, const void* src, bool real) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = real ? 16 : 0;                           // 0 bytes read: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// cap * tanh(s / cap) with tanh(x) = 1 - 2 / (exp(2x) + 1) from the fast exponential and reciprocal: the absolute error of
+// the capped score stays near 1e-6 cap, far below what the bfloat16 operands of the score leave.  `cap2` = 2 / cap.
+__device__ __forceinline__ float soft_cap_fast(float s, float cap, float cap2) {
+  return cap > 0.f ? cap - 2.f * cap * __fdividef(1.f, __expf(s * cap2) + 1.f) : s;
+}
+
+// DEC: the tile has at most 16 rows (a single token's heads of one kv head).  All warps then work on rows 0 .. 15 and share
+// out a tile's keys (warp w takes keys 16 w .. 16 w + 15), each with a softmax state of its own; the four states are merged
+// through shared memory at the end.  Otherwise warp w owns rows 16 w .. 16 w + 15 and walks all keys of a tile.
+template <int VT, bool DEC>
+__global__ void __launch_bounds__(kMmaWarps * 32)
+diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+                          const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_tables, int max_pages,
+                          const int* __restrict__ seq_starts, const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
+                          float* __restrict__ part, int first_token, int seq0, int n_seqs, int H, int G, int dim, int vdim,
+                          int page_size, int window, int split_keys, int n_splits, float scale, float cap, float lambda,
+                          float eps, float out_scale) {
+  chain_wait();
+  constexpr int kRows = DEC ? 16 : kMmaRows;        // rows of the block's tile
+  constexpr int NTW = DEC ? 2 : 8;                   // 8-key tiles of a 64-key tile that one warp makes scores for
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int kw = 2 * dim, kst = kw + 8, vst = 16 * VT + 8;         // row strides in elements (16 bytes of padding)
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [kRows][kst]
+  __nv_bfloat16* Ks = Qs + kRows * kst;                            // [2][64][kst]
+  __nv_bfloat16* Vs = Ks + 2 * kMmaKeys * kst;                     // [2][64][vst]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int kvh = blockIdx.y, rep = H / G, split = blockIdx.z;
+  const int row0_w = DEC ? 0 : 16 * warp, key0_w = DEC ? 16 * warp : 0;
+
+  // which sequence, which of its row tiles: a sequence's rows are its (token, head of this kv head) pairs, heads fastest
+  int tile = blockIdx.x, s = seq0, rows_s = 0;
+  for (;; ++s) {
+    if (s >= seq0 + n_seqs) return;
+    rows_s = (seq_starts[s + 1] - seq_starts[s]) * rep;
+    const int tiles = (rows_s + kRows - 1) / kRows;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  const int tok_s = seq_starts[s], r0 = tile * kRows;
+  const int valid = min(kRows, rows_s - r0);
+  auto token_of = [&](int r) { return tok_s + (r0 + r) / rep; };
+  auto head_of = [&](int r) { return kvh * rep + (r0 + r) % rep; };
+  const int pos_first = positions[token_of(0)], pos_last = positions[token_of(valid - 1)];
+  // a window moves the first key; splits stay at multiples of their size, counted from the one that holds it
+  const int lo = first_visible_key(pos_first, window);
+  const int base = n_splits > 1 ? (lo / split_keys + split) * split_keys : 0;
+  const int begin = n_splits > 1 ? max(lo, base) : lo;
+  const int end = n_splits > 1 ? min(pos_last + 1, base + split_keys) : pos_last + 1;
+  const int* bt = block_tables + (size_t)s * max_pages;
+
+  // queries of the tile (rows past the valid ones: zeros)
+  const int q_chunks = kw / 8;
+  for (int idx = threadIdx.x; idx < kRows * q_chunks; idx += blockDim.x) {
+    const int r = idx / q_chunks, c = idx % q_chunks;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid) v = *reinterpret_cast<const uint4*>(q + ((size_t)token_of(r) * H + head_of(r)) * kw + 8 * c);
+    *reinterpret_cast<uint4*>(Qs + r * kst + 8 * c) = v;
+  }
+  if (16 * VT > vdim) {          // the copies never touch these columns of the value stages
+    const int extra = 16 * VT - vdim;
+    for (int idx = threadIdx.x; idx < 2 * kMmaKeys * extra; idx += blockDim.x)
+      Vs[(idx / extra) * vst + vdim + idx % extra] = __float2bfloat16_rn(0.f);
+  }
+  // A tile's rows are shared out by warp (rows warp, warp + 4, ...).  Lane j looks up the page of the warp's j-th row, so
+  // that the sixteen lookups are in flight together; then the lanes copy a row's 16-byte pieces, keys and values side by side.
+  const int v_chunks = vdim / 8, kv_chunks = q_chunks + v_chunks;
+  auto load_tile = [&](int k0, int stage) {
+    __nv_bfloat16* kd = Ks + stage * kMmaKeys * kst;
+    __nv_bfloat16* vd = Vs + stage * kMmaKeys * vst;
+    const int my_key = k0 + warp + kMmaWarps * (lane & 15);
+    long long my_row = -1;                                       // (page * G + kv head) * page_size + offset, or -1 past the end
+    if (my_key < end) my_row = ((long long)bt[my_key / page_size] * G + kvh) * page_size + my_key % page_size;
+#pragma unroll 4
+    for (int j = 0; j < kMmaKeys / kMmaWarps; ++j) {
+      const long long row = __shfl_sync(0xffffffffu, my_row, j);
+      const bool real = row >= 0;
+      const int r = warp + kMmaWarps * j;
+      const __nv_bfloat16* ksrc = k_pages + (real ? row : 0) * kw;
+      const __nv_bfloat16* vsrc = v_pages + (real ? row : 0) * vdim;
+      for (int c = lane; c < kv_chunks; c += 32) {
+        if (c < q_chunks) copy16(kd + r * kst + 8 * c, ksrc + 8 * c, real);
+        else copy16(vd + r * vst + 8 * (c - q_chunks), vsrc + 8 * (c - q_chunks), real);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  const int r_lo = row0_w + g, r_hi = r_lo + 8;                     // this thread's two rows of the tile
+  const int pos_lo = r_lo < valid ? positions[token_of(r_lo)] : -1, pos_hi = r_hi < valid ? positions[token_of(r_hi)] : -1;
+  const int low_lo = first_visible_key(pos_lo, window), low_hi = first_visible_key(pos_hi, window);
+  // what the warp's rows see at most and at least: a tile of keys inside [w_low_max, w_pos_min] needs no mask
+  const int w_last = min(valid - 1, row0_w + 15);
+  const int w_pos_max = row0_w < valid ? positions[token_of(w_last)] : -1, w_pos_min = row0_w < valid ? positions[token_of(row0_w)] : -1;
+  const int w_low_min = first_visible_key(w_pos_min, window), w_low_max = first_visible_key(w_pos_max, window);
+  const bool w_full = row0_w + 15 < valid;                          // (rows past the valid ones must stay masked)
+  const float cap2 = cap > 0.f ? 2.f / cap : 0.f;
+  float m[2][2], l[2][2];                                           // [map][row]: running maximum, this thread's share of the sum
+  float o[2][2 * VT][4];
+#pragma unroll
+  for (int mp = 0; mp < 2; ++mp) {
+    m[mp][0] = m[mp][1] = -INFINITY;
+    l[mp][0] = l[mp][1] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2 * VT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[mp][nt][i] = 0.f;
+  }
+
+  const int n_tiles = begin < end ? (end - begin + kMmaKeys - 1) / kMmaKeys : 0;
+  if (n_tiles > 0) load_tile(begin, 0);
+  for (int it = 0; it < n_tiles; ++it) {
+    const int k0 = begin + it * kMmaKeys, stage = it & 1;
+    if (it + 1 < n_tiles) {
+      load_tile(k0 + kMmaKeys, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const __nv_bfloat16* Kt = Ks + stage * kMmaKeys * kst;
+    const __nv_bfloat16* Vt = Vs + stage * kMmaKeys * vst;
+    const int kf = k0 + key0_w, kl = kf + 8 * NTW - 1;              // the first and last key this warp looks at in the tile
+    // (a warp whose rows all lie before its first key, or whose windows all lie behind its last, has nothing here)
+    const bool idle = row0_w >= valid || kf > w_pos_max || kl < w_low_min || kf >= end;
+    const bool plain = w_full && kf >= w_low_max && kl <= w_pos_min && kl < end;      // no key of it is masked for any row
+    if (!idle) {
+#pragma unroll
+      for (int mp = 0; mp < 2; ++mp) {
+        float sc[NTW][4];
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
+        const __nv_bfloat16* qa = Qs + (row0_w + (lane & 7) + 8 * ((lane >> 3) & 1)) * kst + mp * dim + 8 * (lane >> 4);
+        for (int kk = 0; kk < dim; kk += 16) {
+          uint32_t a[4];
+          ldsm4(a, qa + kk);
+#pragma unroll
+          for (int np = 0; np < NTW / 2; ++np) {      // a pair of 8-key tiles per ldmatrix: 16 keys, k kk .. kk + 15
+            uint32_t b[4];
+            ldsm4(b, Kt + (key0_w + 16 * np + (lane & 7) + 8 * (lane >> 4)) * kst + mp * dim + kk + 8 * ((lane >> 3) & 1));
+            mma16816(sc[2 * np], a, b[0], b[1]);
+            mma16816(sc[2 * np + 1], a, b[2], b[3]);
+          }
+        }
+        // scale, cap, mask; the rows' maxima
+        float top[2] = {m[mp][0], m[mp][1]};
+        if (plain) {
+#pragma unroll
+          for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float v = soft_cap_fast(sc[nt][i] * scale, cap, cap2);
+              sc[nt][i] = v;
+              top[i >> 1] = fmaxf(top[i >> 1], v);
+            }
+        } else {
+#pragma unroll
+          for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int key = kf + 8 * nt + 2 * tq + (i & 1);
+              const int row_pos = i < 2 ? pos_lo : pos_hi, row_low = i < 2 ? low_lo : low_hi;
+              float v = soft_cap_fast(sc[nt][i] * scale, cap, cap2);
+              if (key > row_pos || key < row_low || key >= end) v = -INFINITY;
+              sc[nt][i] = v;
+              top[i >> 1] = fmaxf(top[i >> 1], v);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 1));
+          top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 2));
+        }
+        float alpha[2], shift[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          alpha[r] = (top[r] == -INFINITY || m[mp][r] == -INFINITY) ? (top[r] == -INFINITY ? 1.f : 0.f) : __expf(m[mp][r] - top[r]);
+          shift[r] = top[r] == -INFINITY ? 0.f : top[r];             // (exp(-inf - 0) = 0 for a row that has seen no key yet)
+          m[mp][r] = top[r];
+          l[mp][r] *= alpha[r];
+        }
+        uint32_t pa[NTW / 2][4];               // the weights as A operands: [k-step of 16 keys][fragment]
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) {
+          float p[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            p[i] = __expf(sc[nt][i] - shift[i >> 1]);
+            l[mp][i >> 1] += p[i];
+          }
+          pa[nt >> 1][2 * (nt & 1)] = pack_bf16(p[0], p[1]);
+          pa[nt >> 1][2 * (nt & 1) + 1] = pack_bf16(p[2], p[3]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2 * VT; ++nt) {
+          o[mp][nt][0] *= alpha[0]; o[mp][nt][1] *= alpha[0];
+          o[mp][nt][2] *= alpha[1]; o[mp][nt][3] *= alpha[1];
+        }
+#pragma unroll
+        for (int ks = 0; ks < NTW / 2; ++ks) {
+#pragma unroll
+          for (int pr = 0; pr < VT; ++pr) {
+            uint32_t b[4];
+            ldsm4t(b, Vt + (key0_w + 16 * ks + (lane & 7) + 8 * ((lane >> 3) & 1)) * vst + 16 * pr + 8 * (lane >> 4));
+            mma16816(o[mp][2 * pr], pa[ks], b[0], b[1]);
+            mma16816(o[mp][2 * pr + 1], pa[ks], b[2], b[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // each row's sums live in a quad of lanes
+#pragma unroll
+  for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l[mp][r] += __shfl_xor_sync(0xffffffffu, l[mp][r], 1);
+      l[mp][r] += __shfl_xor_sync(0xffffffffu, l[mp][r], 2);
+    }
+  const int vpad = 64 * (vdim <= 64 ? 1 : (vdim <= 128 ? 2 : 4));   // (the layout of the general kernel's split states)
+  if constexpr (DEC) {
+    // The warps' states of the 16 rows go to shared memory (over the stages: every warp has left the loop), float
+    // [warp][map][row][16 VT + 2] with the maximum and the sum behind a row; then warp w finishes rows w, w + 4, ...
+    const int mst = 16 * VT + 2;
+    float* M = reinterpret_cast<float*>(smem_raw);
+    __syncthreads();             // (a block without a tile of keys has not met since it wrote the queries)
+#pragma unroll
+    for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float* dst = M + ((size_t)(warp * 2 + mp) * 16 + g + 8 * r) * mst;
+#pragma unroll
+        for (int nt = 0; nt < 2 * VT; ++nt) {
+          dst[8 * nt + 2 * tq] = o[mp][nt][2 * r];
+          dst[8 * nt + 2 * tq + 1] = o[mp][nt][2 * r + 1];
+        }
+        if (tq == 0) { dst[16 * VT] = m[mp][r]; dst[16 * VT + 1] = l[mp][r]; }
+      }
+    __syncthreads();
+    for (int row = warp; row < valid; row += kMmaWarps) {
+      float wgt[2][kMmaWarps], top[2], sum[2];
+#pragma unroll
+      for (int mp = 0; mp < 2; ++mp) {
+        top[mp] = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w) top[mp] = fmaxf(top[mp], M[((size_t)(w * 2 + mp) * 16 + row) * mst + 16 * VT]);
+        sum[mp] = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w) {
+          const float* src = M + ((size_t)(w * 2 + mp) * 16 + row) * mst + 16 * VT;
+          wgt[mp][w] = src[0] == -INFINITY ? 0.f : __expf(src[0] - top[mp]);
+          sum[mp] = fmaf(src[1], wgt[mp][w], sum[mp]);
+        }
+      }
+      float acc[2][(16 * VT + 31) / 32];
+#pragma unroll
+      for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+        for (int i = 0; i < (16 * VT + 31) / 32; ++i) {
+          const int c = lane + 32 * i;
+          float v = 0.f;
+          if (c < 16 * VT) {
+#pragma unroll
+            for (int w = 0; w < kMmaWarps; ++w) v = fmaf(M[((size_t)(w * 2 + mp) * 16 + row) * mst + c], wgt[mp][w], v);
+          }
+          acc[mp][i] = v;
+        }
+      const int tok = token_of(row), head = head_of(row);
+      if (n_splits > 1) {
+        float* dst = part + ((size_t)((tok - first_token) * H + head) * n_splits + split) * (4 + 2 * vpad);
+        if (lane == 0) { dst[0] = top[0]; dst[1] = sum[0]; dst[2] = top[1]; dst[3] = sum[1]; }
+#pragma unroll
+        for (int i = 0; i < (16 * VT + 31) / 32; ++i) {
+          const int c = lane + 32 * i;
+          if (c < vdim) { dst[4 + c] = acc[0][i]; dst[4 + vpad + c] = acc[1][i]; }
+        }
+        continue;
+      }
+      const float r1 = 1.f / sum[0], r2 = lambda / sum[1];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < (16 * VT + 31) / 32; ++i) {
+        acc[0][i] = acc[0][i] * r1 - acc[1][i] * r2;
+        if (lane + 32 * i < vdim) ss = fmaf(acc[0][i], acc[0][i], ss);
+      }
+      const float f = rsqrtf(warp_sum(ss) / (float)vdim + eps) * out_scale;
+      __nv_bfloat16* dst = out + ((size_t)tok * H + head) * vdim;
+#pragma unroll
+      for (int i = 0; i < (16 * VT + 31) / 32; ++i) {
+        const int c = lane + 32 * i;
+        if (c < vdim) dst[c] = __float2bfloat16_rn(acc[0][i] * f);
+      }
+    }
+    return;
+  }
+  if (n_splits > 1) {          // the states of this split
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = r ? r_hi : r_lo;
+      if (row >= valid) continue;
+      float* dst = part + ((size_t)((token_of(row) - first_token) * H + head_of(row)) * n_splits + split) * (4 + 2 * vpad);
+      if (tq == 0) { dst[0] = m[0][r]; dst[1] = l[0][r]; dst[2] = m[1][r]; dst[3] = l[1][r]; }
+#pragma unroll
+      for (int nt = 0; nt < 2 * VT; ++nt) {
+        const int c = 8 * nt + 2 * tq;
+        if (c < vdim) {
+          *reinterpret_cast<float2*>(dst + 4 + c) = make_float2(o[0][nt][2 * r], o[0][nt][2 * r + 1]);
+          *reinterpret_cast<float2*>(dst + 4 + vpad + c) = make_float2(o[1][nt][2 * r], o[1][nt][2 * r + 1]);
+        }
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const float r1 = 1.f / l[0][r], r2 = lambda / l[1][r];
+    float ss = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2 * VT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float v = o[0][nt][2 * r + i] * r1 - o[1][nt][2 * r + i] * r2;
+        o[0][nt][2 * r + i] = v;
+        if (8 * nt + 2 * tq + i < vdim) ss = fmaf(v, v, ss);
+      }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    const float f = rsqrtf(ss / (float)vdim + eps) * out_scale;
+    const int row = r ? r_hi : r_lo;
+    if (row < valid) {
+      __nv_bfloat16* dst = out + ((size_t)token_of(row) * H + head_of(row)) * vdim;
+#pragma unroll
+      for (int nt = 0; nt < 2 * VT; ++nt) {
+        const int c = 8 * nt + 2 * tq;
+        if (c < vdim) *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(o[0][nt][2 * r] * f, o[0][nt][2 * r + 1] * f);
+      }
+    }
+  }
+}
+
+template <int VT, bool DEC>
+int launch_mma(cudaStream_t st, const void* q, const void* k_pages, const void* v_pages, const int* block_tables, int max_pages,
+               const int* seq_starts, const int* positions, void* out, float* part, int first_token, int n_tokens, int seq0,
+               int n_seqs, int n_tiles, int H, int G, int dim, int vdim, int page_size, int window, int split_keys, int n_splits,
+               float scale, float cap, float lambda, float eps, float out_scale) {
+  const int rows = DEC ? 16 : kMmaRows;
+  size_t smem = sizeof(__nv_bfloat16) * ((size_t)(rows + 2 * kMmaKeys) * (2 * dim + 8) + 2 * (size_t)kMmaKeys * (16 * VT + 8));
+  if (DEC) smem = std::max(smem, sizeof(float) * kMmaWarps * 2 * 16 * (size_t)(16 * VT + 2));     // (the merge of the warps' states)
+  auto kern = diff_attention_mma_kernel<VT, DEC>;
+  if (smem > 227 * 1024) return fail(ERB_ERR_UNSUPPORTED, "diff_attention_mma: maps of %d entries need %zu bytes of shared memory", dim, smem);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "diff_attention_mma: %s", cudaGetErrorString(e));
+  }
+  launch_chained(kern, dim3(n_tiles, G, n_splits), dim3(kMmaWarps * 32), smem, st, (const __nv_bfloat16*)q,
+                 (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_tables, max_pages, seq_starts, positions,
+                 (__nv_bfloat16*)out, part, first_token, seq0, n_seqs, H, G, dim, vdim, page_size, window, split_keys, n_splits, scale,
+                 cap, lambda, eps, out_scale);
+  int rc = check_launch("diff_attention_mma");
+  if (rc || n_splits == 1) return rc;
+  const int n_rows = n_tokens * H;
+  auto merge = [&](auto kernel) {
+    launch_chained(kernel, dim3((n_rows + kWarps - 1) / kWarps), dim3(kWarps * 32), 0, st, (const float*)part, (__nv_bfloat16*)out,
+                   first_token, n_rows, H, vdim, n_splits, lambda, eps, out_scale);
+  };
+  if (vdim <= 64) merge(diff_combine_kernel<__nv_bfloat16, 1>); else merge(diff_combine_kernel<__nv_bfloat16, 2>);
+  return check_launch("diff_combine");
+}
+#endif  // ERB_ELEM == 1
+
 template <int VI>
 int launch_attention(cudaStream_t st, const elem_t* q, const elem_t* k_pages, const elem_t* v_pages, const int* block_tables,
                      int max_pages, const int* seq_of_token, const int* positions, elem_t* out, float* part, int first_token,
@@ -379,4 +794,35 @@ ERB_EXPORT int erb_diff_attention(const void* q, const void* k_pages, const void
   if (vdim <= 128) return ERB_DIFF(2);
   return ERB_DIFF(4);
 #undef ERB_DIFF
+}
+
+// The tensor-core form (bfloat16 build only): sequences seq0 .. seq0 + n_seqs of the batch, whose rows are tokens
+// seq_starts[s] .. seq_starts[s + 1] (tokens first_token .. first_token + n_tokens in all); `n_tiles` = sum over them of
+// ceil(tokens * (H / G) / tile_rows), tile_rows 64 (portions) or 16 (single tokens: the warps share out a tile's keys).  With n_splits > 1 (single tokens) `part` takes the splits' states as for erb_diff_attention.
+// Needs maps of a multiple of 16 entries and value rows of a multiple of 8 entries, at most 128.
+ERB_EXPORT int erb_diff_attention_mma(const void* q, const void* k_pages, const void* v_pages, const int* block_tables,
+                                      int max_pages, const int* seq_starts, const int* positions, void* out, float* part,
+                                      int first_token, int n_tokens, int seq0, int n_seqs, int n_tiles, int tile_rows, int H, int G,
+                                      int dim, int vdim, int page_size, int window, int split_keys, int n_splits, float scale,
+                                      float cap, float lambda, float eps, float out_scale, void* stream) {
+#if ERB_ELEM == 1
+  if (n_seqs <= 0 || n_tiles <= 0) return ERB_OK;
+  if (H <= 0 || G <= 0 || H % G || dim <= 0 || dim % 16 || vdim <= 0 || vdim % 8 || vdim > 128 || page_size <= 0 || window < 0 ||
+      ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || ((uintptr_t)out & 3) || n_splits < 1 ||
+      (n_splits > 1 && (!part || split_keys <= 0 || ((uintptr_t)part & 7))) || (tile_rows != 16 && tile_rows != 64))
+    return fail(ERB_ERR_UNSUPPORTED, "diff_attention_mma: sizes (maps of %d, values of %d) or alignment not supported", dim, vdim);
+  cudaStream_t st = (cudaStream_t)stream;
+#define ERB_DIFF_MMA(VT) (tile_rows == 16 ? ERB_DIFF_MMA2(VT, true) : ERB_DIFF_MMA2(VT, false))
+#define ERB_DIFF_MMA2(VT, DEC) launch_mma<VT, DEC>(st, q, k_pages, v_pages, block_tables, max_pages, seq_starts, positions, out, part,         \
+    first_token, n_tokens, seq0, n_seqs, n_tiles, H, G, dim, vdim, page_size, window, split_keys, n_splits, scale, cap, lambda, eps, \
+    out_scale)
+  if (vdim <= 32) return ERB_DIFF_MMA(2);
+  if (vdim <= 64) return ERB_DIFF_MMA(4);
+  if (vdim <= 96) return ERB_DIFF_MMA(6);
+  return ERB_DIFF_MMA(8);
+#undef ERB_DIFF_MMA
+#undef ERB_DIFF_MMA2
+#else
+  return fail(ERB_ERR_UNSUPPORTED, "diff_attention_mma: the tensor-core form is built for bfloat16 only");
+#endif
 }

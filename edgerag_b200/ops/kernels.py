@@ -95,6 +95,9 @@ _SIGNATURES = {
     "erb_diff_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_float,
                            c_void_p],
+    "erb_diff_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                               c_float, c_float, c_float, c_void_p],
     "erb_conv_silu": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p],
     "erb_conv_state_update": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -1073,6 +1076,56 @@ def diff_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
           seq_of_token.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(part), int(first_token), int(n_tokens), int(n_heads),
           int(n_kv), two_dim // 2, v_dim, page_size, int(window), int(split_keys), int(n_splits), float(scale), float(softcap),
           float(lam), float(eps), float(out_scale), _stream())
+
+
+DIFF_MMA_ROWS = 64         # (token, head) rows of one sequence and kv head that a block of the tensor-core form owns
+DIFF_MMA_TOKEN_ROWS = 16   # the same for single tokens: the block's warps share out the keys instead of the rows
+
+
+def diff_mma_supported(dtype: torch.dtype, dim: int, v_dim: int) -> bool:
+    """Whether the tensor-core form of the differential attention takes these sizes: bfloat16, maps of a multiple of 16
+    entries, value rows of a multiple of 8 entries up to 128, and its three tiles within an SM's shared memory."""
+    vt = 2 if v_dim <= 32 else 4 if v_dim <= 64 else 6 if v_dim <= 96 else 8
+    smem = 2 * ((64 + 2 * 64) * (2 * dim + 8) + 2 * 64 * (16 * vt + 8))
+    return dtype == torch.bfloat16 and dim % 16 == 0 and v_dim % 8 == 0 and 0 < v_dim <= 128 and smem <= 227 * 1024
+
+
+def diff_mma_tiles(q_lens, heads_per_kv: int, tile_rows: int = DIFF_MMA_ROWS) -> int:
+    """Blocks of ``tile_rows`` (token, head) rows per kv head that sequences of these many new tokens need."""
+    return sum(-(-int(n) * heads_per_kv // tile_rows) for n in q_lens)
+
+
+def diff_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
+                       seq_starts: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float,
+                       lam: float, eps: float, out_scale: float, first_seq: int, n_seqs: int, first_token: int, n_tokens: int,
+                       n_tiles: int, *, window: int = 0, softcap: float = 0.0, split_keys: int = 0, n_splits: int = 1,
+                       part: torch.Tensor | None = None, tile_rows: int = DIFF_MMA_ROWS) -> None:
+    """``diff_attention`` on tensor cores for sequences ``first_seq .. first_seq + n_seqs`` of the batch (their tokens are
+    rows ``first_token .. first_token + n_tokens``, sequence ``s`` owning ``seq_starts[s] .. seq_starts[s + 1]`` and row
+    ``s`` of ``block_tables``); ``n_tiles = diff_mma_tiles(new tokens per sequence, heads per kv head, tile_rows)``.
+    ``tile_rows`` 64: a block's warps share out the rows (portions); 16: they share out the keys (single tokens with at
+    most 16 heads per kv head).  Splits as for ``diff_attention`` (single tokens)."""
+    _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", torch.bfloat16); _need(v_pages, "v_pages", torch.bfloat16)
+    _need(out, "out", torch.bfloat16); _need(block_tables, "block_tables", torch.int32); _need(seq_starts, "seq_starts", torch.int32)
+    _need(positions, "positions", torch.int32)
+    n = q.shape[0]
+    n_kv, page_size, two_dim = k_pages.shape[1:]
+    v_dim = v_pages.shape[3]
+    if two_dim % 2 or q.shape[1] != n_heads * two_dim or out.shape != (n, n_heads * v_dim) or n_heads % n_kv or \
+            tuple(v_pages.shape[1:3]) != (n_kv, page_size) or not diff_mma_supported(q.dtype, two_dim // 2, v_dim):
+        raise KernelError("diff_attention_mma: q, pages and out disagree, or the sizes are not supported")
+    if first_seq < 0 or first_seq + n_seqs > block_tables.shape[0] or seq_starts.numel() < first_seq + n_seqs + 1 or \
+            first_token < 0 or first_token + n_tokens > n or positions.numel() < n:
+        raise KernelError("diff_attention_mma: the sequence or token range lies outside the batch")
+    _need(part, "part", torch.float32)
+    if n_splits > 1 and (part is None or split_keys <= 0 or part.numel() < n_tokens * n_heads * n_splits * diff_part_floats(v_dim)):
+        raise KernelError("diff_attention_mma: the scratch for the splits is too small")
+    fn = _fn("diff_attention", "bfloat16", "erb_diff_attention_mma")
+    fn._erb_own = 2 if n_splits > 1 else 1
+    _call(fn, q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
+          seq_starts.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(part), int(first_token), int(n_tokens), int(first_seq),
+          int(n_seqs), int(n_tiles), int(tile_rows), int(n_heads), int(n_kv), two_dim // 2, v_dim, page_size, int(window),
+          int(split_keys), int(n_splits), float(scale), float(softcap), float(lam), float(eps), float(out_scale), _stream())
 
 
 # --- state-space mixer -------------------------------------------------------------------------

@@ -351,6 +351,12 @@ def latent_attention(a) -> dict:
         pos = torch.arange(a.past, total, dtype=torch.int32, device="cuda")
         seq_of = torch.zeros(n, dtype=torch.int32, device="cuda")
         split, n_splits = 0, 1
+    window = int(getattr(a, "window", 0) or 0)
+    reach = min(total, window) if window else total          # keys a single token reads
+    if decode and window and not a.split:
+        want = max(1, min(-(-2 * kernels._sms(q.device) // blocks), -(-reach // 64), kernels.LATENT_MAX_SPLITS))
+        split = -(-(-(-reach // want)) // 64) * 64
+        n_splits = min(-(-total // split), (window - 1) // split + 2)
     part = torch.empty(max(1, kernels.latent_scratch_floats(n, a.heads, a.rank, n_splits)), device="cuda")
     state = {"i": 0}
 
@@ -361,25 +367,96 @@ def latent_attention(a) -> dict:
         tiles = kernels.latent_mma_tiles(q_lens, a.heads, mt)
         starts = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
         if decode and not a.split:
-            want = max(1, min(-(-kernels._sms(q.device) // tiles), -(-total // 64), kernels.LATENT_MAX_SPLITS))
-            split = -(-(-(-total // want)) // 64) * 64
-            n_splits = -(-total // split)
+            want = max(1, min(-(-kernels._sms(q.device) // tiles), -(-reach // 64), kernels.LATENT_MAX_SPLITS))
+            split = -(-(-(-reach // want)) // 64) * 64
+            n_splits = -(-total // split) if not window else min(-(-total // split), (window - 1) // split + 2)
             part = torch.empty(max(1, kernels.latent_scratch_floats(n, a.heads, a.rank, n_splits)), device="cuda")
 
     def fn():
         state["i"] = (state["i"] + 1) % reps
         if mma:
             kernels.latent_attention_mma(q, pools[state["i"]], tables, starts, pos, out, 1.0, 0, n_seqs, 0, n, tiles, mt,
-                                         split_keys=split, n_splits=n_splits, part=part if n_splits > 1 else None)
+                                         split_keys=split, n_splits=n_splits, part=part if n_splits > 1 else None, window=window)
         else:
             kernels.latent_attention(q, pools[state["i"]], tables, seq_of, pos, out, 1.0, 0, n, split_keys=split,
-                                     n_splits=n_splits, part=part if n_splits > 1 else None)
+                                     n_splits=n_splits, part=part if n_splits > 1 else None, window=window)
 
     us = _time(fn, max(a.iters, 2 * reps), a.warmup)
-    nbytes = n_seqs * total * dk * item
-    pairs = n * total if decode else a.tokens * a.past + a.tokens * (a.tokens + 1) / 2
+    nbytes = n_seqs * reach * dk * item
+    pairs = n * reach if decode else _seen_pairs(a.tokens, a.past, window)
     flops = 2.0 * a.heads * (dk + a.rank) * pairs
     return {"case": "latent-attention", "kernel": "mma" if mma else "general", "mode": "decode" if decode else "prefill", "splits": n_splits, "us": round(us, 2),
+            "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4),
+            "tflops": round(flops / us / 1e6, 2), "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4),
+            "from_dram": bool(decode and (a.cold or nbytes > 126e6))}
+
+
+def _seen_pairs(tokens: int, past: int, window: int) -> float:
+    """(query, key) pairs that ``tokens`` queries after ``past`` cached tokens see, under a window or without one."""
+    if not window:
+        return tokens * past + tokens * (tokens + 1) / 2
+    return float(sum(min(window, past + i + 1) for i in range(tokens)))
+
+
+def diff_attention(a) -> dict:
+    """The differential-attention kernel: single tokens at the end of ``context`` cached tokens (bound by the keys and
+    values of their windows), or ``tokens`` prompt tokens after ``past`` (bound by its arithmetic: per seen pair and
+    head, two score products of ``dim`` and two value sums of ``vdim``)."""
+    dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
+    item = 2 if dtype == torch.bfloat16 else 4
+    H, G, d, dv, window = a.heads, a.kv_heads, a.dim, a.vdim, int(a.window or 0)
+    decode = a.tokens <= 0
+    n_seqs = a.batch if decode else 1
+    total = a.context if decode else a.past + a.tokens
+    n = n_seqs if decode else a.tokens
+    pages_per = -(-total // a.page)
+    reach = min(total, window) if window else total
+    reps = max(2, int(300e6 // (n_seqs * reach * G * (2 * d + dv) * item)) + 1) if (decode and a.cold) else 1
+    kp = [torch.randn((n_seqs * pages_per, G, a.page, 2 * d), device="cuda").to(dtype) for _ in range(reps)]
+    vp = [torch.randn((n_seqs * pages_per, G, a.page, dv), device="cuda").to(dtype) for _ in range(reps)]
+    tables = torch.randperm(n_seqs * pages_per).to(torch.int32).view(n_seqs, pages_per).cuda()
+    q = (torch.randn((n, H * 2 * d), device="cuda") * d ** -0.5).to(dtype)
+    out = torch.empty((n, H * dv), device="cuda", dtype=dtype)
+    split, n_splits = 0, 1
+    if decode:
+        pos = torch.full((n,), total - 1, dtype=torch.int32, device="cuda")
+        seq_of = torch.arange(n, dtype=torch.int32, device="cuda")
+        blocks = -(-n * H // 4)
+        want = max(1, min(-(-2 * kernels._sms(q.device) // blocks), -(-reach // 64), 64))
+        split = a.split or -(-(-(-reach // want)) // 64) * 64
+        n_splits = -(-total // split) if not window else min(-(-total // split), (window - 1) // split + 2)
+    else:
+        pos = torch.arange(a.past, total, dtype=torch.int32, device="cuda")
+        seq_of = torch.zeros(n, dtype=torch.int32, device="cuda")
+    mma = getattr(a, "kernel", "mma") == "mma" and kernels.diff_mma_supported(dtype, d, dv)
+    if mma:
+        q_lens = [1] * n if decode else [a.tokens]
+        tile_rows = 16 if (decode and H // G <= 16) else 64
+        tiles = kernels.diff_mma_tiles(q_lens, H // G, tile_rows)
+        starts = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+        if decode and not a.split:      # as the mixer plans: a block per (sequence, kv head, split)
+            want = max(1, min(-(-2 * kernels._sms(q.device) // max(1, n * G)), -(-reach // 64), 64))
+            split = -(-(-(-reach // want)) // 64) * 64
+            n_splits = -(-total // split) if not window else min(-(-total // split), (window - 1) // split + 2)
+    part = torch.empty(max(1, n * H * n_splits * kernels.diff_part_floats(dv)), device="cuda")
+    state = {"i": 0}
+
+    def fn():
+        state["i"] = (state["i"] + 1) % reps
+        if mma:
+            kernels.diff_attention_mma(q, kp[state["i"]], vp[state["i"]], tables, starts, pos, out, H, d ** -0.5, 0.3, 1e-6, 0.5, 0,
+                                       n_seqs, 0, n, tiles, window=window, softcap=float(a.softcap), split_keys=split,
+                                       n_splits=n_splits, part=part if n_splits > 1 else None, tile_rows=tile_rows)
+            return
+        kernels.diff_attention(q, kp[state["i"]], vp[state["i"]], tables, seq_of, pos, out, H, d ** -0.5, 0.3, 1e-6, 0.5, 0, n,
+                               window=window, softcap=float(a.softcap), split_keys=split, n_splits=n_splits,
+                               part=part if n_splits > 1 else None)
+
+    us = _time(fn, max(a.iters, 2 * reps), a.warmup)
+    nbytes = n_seqs * reach * G * (2 * d + dv) * item
+    pairs = n * reach if decode else _seen_pairs(a.tokens, a.past, window)
+    flops = 2.0 * H * (2 * d + 2 * dv) * pairs
+    return {"case": "diff-attention", "kernel": "mma" if mma else "general", "mode": "decode" if decode else "prefill", "splits": n_splits, "us": round(us, 2),
             "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4),
             "tflops": round(flops / us / 1e6, 2), "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4),
             "from_dram": bool(decode and (a.cold or nbytes > 126e6))}
@@ -458,6 +535,8 @@ def routed_experts(a) -> dict:
 
     tc = kernels.moe_tc_supported(dtype, h, ff) and not getattr(a, "general", False)     # as the feed-forward part chooses
     tile_rows = kernels.moe_tc_tile_rows(n, E, top) if tc else 0
+    if getattr(a, "ungated", False):
+        return _routed_experts_ungated(a, x, router, wgu, wd, lists, score, act, parts, tc, tile_rows, rotate, reps, item)
     kernels.moe_route(x, router, top, lists, score, tile_rows)
     used = int((lists[2 * n * top: 2 * n * top + E] > 0).sum())     # experts that some row chose
     us_route = _time(lambda: kernels.moe_route(x, router, top, lists, score, tile_rows), a.iters, a.warmup)
@@ -490,6 +569,40 @@ def routed_experts(a) -> dict:
     return {"case": "routed-experts", "tokens": n, "experts": E, "top": top, "ff": ff, "width": h, "experts_used": used,
             "tensor_cores": bool(tc), "tile_rows": tile_rows, "route_us": round(us_route, 2), "gather_us": round(us_gather, 2), "gate_up": line(us_up, flops_up, bytes_up), "down": line(us_down, flops_down, bytes_down),
             "dense_gate_up": line(us_dense_up, flops_up, dense_bytes_up), "dense_down": line(us_dense_down, flops_down, dense_bytes_down)}
+
+
+def _routed_experts_ungated(a, x, router, wgu, wd, lists, score, act, parts, tc, tile_rows, rotate, reps, item) -> dict:
+    """The same for experts without a gate branch (one up product with the square of relu), softmax scores over groups
+    of experts and the weight on the down product's output."""
+    n, E, top, ff, h = a.tokens, a.experts, a.top, a.ff, a.width
+    groups = tuple(a.groups) if getattr(a, "groups", None) else None
+    wu = [w[:, :ff].contiguous() for w in wgu]
+    route = lambda: kernels.moe_route(x, router, top, lists, score, tile_rows, scores="softmax", groups=groups)   # noqa: E731
+    route()
+    used = int((lists[2 * n * top: 2 * n * top + E] > 0).sum())
+    us_route = _time(route, a.iters, a.warmup)
+    us_gather = 0.0
+    if tc:
+        xs = torch.empty((n * top, h), dtype=x.dtype, device="cuda")
+        kernels.moe_tc_gather(x, lists, None, E, top, xs)
+        us_gather = _time(lambda: kernels.moe_tc_gather(x, lists, None, E, top, xs), a.iters, a.warmup)
+        us_up = _time(lambda: kernels.moe_tc_up_act(xs, wu[rotate()], lists, top, tile_rows, act), max(a.iters, 2 * reps), a.warmup)
+        us_down = _time(lambda: kernels.moe_tc_down(act, wd[rotate()], lists, top, tile_rows, parts, out_score=score),
+                        max(a.iters, 2 * reps), a.warmup)
+    else:
+        us_up = _time(lambda: kernels.moe_up_act(x, wu[rotate()], lists, top, act), max(a.iters, 2 * reps), a.warmup)
+        us_down = _time(lambda: kernels.moe_down(act, wd[rotate()], lists, top, parts, out_score=score), max(a.iters, 2 * reps), a.warmup)
+    flops = 2.0 * n * top * ff * h
+    bytes_up = used * ff * h * item + n * h * item + n * top * ff * item
+    bytes_down = used * ff * h * item + n * top * (ff * item + h * 4)
+
+    def line(us, nbytes):
+        return {"us": round(us, 2), "tflops": round(flops / us / 1e6, 2), "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4),
+                "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4)}
+
+    return {"case": "routed-experts", "form": "ungated", "tokens": n, "experts": E, "top": top, "ff": ff, "width": h,
+            "experts_used": used, "tensor_cores": bool(tc), "tile_rows": tile_rows, "route_us": round(us_route, 2),
+            "gather_us": round(us_gather, 2), "up": line(us_up, bytes_up), "down": line(us_down, bytes_down)}
 
 
 def main(argv=None) -> int:
@@ -557,6 +670,22 @@ def main(argv=None) -> int:
     la.add_argument("--split", type=int, default=0)
     la.add_argument("--cold", action="store_true")
     la.add_argument("--kernel", choices=["mma", "general"], default="mma", help="tensor cores (bfloat16) or the general kernel")
+    la.add_argument("--window", type=int, default=0, help="keys a query sees behind itself (0: all)")
+    da = sub.add_parser("diff-attention", parents=[common])
+    da.add_argument("--heads", type=int, default=16)
+    da.add_argument("--kv-heads", type=int, default=4)
+    da.add_argument("--dim", type=int, default=64, help="entries of one score map of a head")
+    da.add_argument("--vdim", type=int, default=128)
+    da.add_argument("--page", type=int, default=16)
+    da.add_argument("--batch", type=int, default=8)
+    da.add_argument("--context", type=int, default=8192)
+    da.add_argument("--tokens", type=int, default=0, help="prompt tokens (0: single tokens of --batch requests)")
+    da.add_argument("--past", type=int, default=0)
+    da.add_argument("--window", type=int, default=1024)
+    da.add_argument("--softcap", type=float, default=30.0)
+    da.add_argument("--split", type=int, default=0)
+    da.add_argument("--cold", action="store_true")
+    da.add_argument("--kernel", choices=["mma", "general"], default="mma", help="tensor cores (bfloat16) or the general kernel")
     ss = sub.add_parser("ssm-scan", parents=[common])
     ss.add_argument("--heads", type=int, default=64)
     ss.add_argument("--head-dim", type=int, default=64)
@@ -578,13 +707,15 @@ def main(argv=None) -> int:
     re.add_argument("--experts", type=int, default=32)
     re.add_argument("--top", type=int, default=4)
     re.add_argument("--general", action="store_true", help="the products on CUDA cores (what float32 runs) instead of tensor cores")
+    re.add_argument("--ungated", action="store_true", help="experts without a gate branch, softmax scores, the weight on the output")
+    re.add_argument("--groups", type=int, nargs=2, default=None, help="with --ungated: (count, keep) of the router's groups")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)
         return 1
     fn = {"decode-attention": decode_attention, "prefill-attention": prefill_attention, "linear": linear,
           "step-kernels": step_kernels, "step-timeline": step_timeline, "latent-attention": latent_attention,
-          "ssm-scan": ssm_scan, "delta-scan": delta_scan, "routed-experts": routed_experts}[a.case]
+          "ssm-scan": ssm_scan, "delta-scan": delta_scan, "routed-experts": routed_experts, "diff-attention": diff_attention}[a.case]
     load_peaks(a.peaks)
     result = fn(a)
     result["peaks"] = PEAKS_FROM

@@ -17,10 +17,11 @@ stretched for long wavelengths (``parts.rope.rotary_frequencies``).  A ``window`
 keys; pages behind every live window go back to the pool.
 
 The cache holds, per token and kv head, both maps' keys side by side (``2 * dim``) and one value row (``v_dim``).
-Three kernels of ``csrc/diff_attention.cu`` do the work between the fused input product and the output product:
+The kernels of ``csrc/diff_attention.cu`` do the work between the fused input product and the output product:
 ``diff_prepare`` (convolution, rotation, cache write), ``diff_attention`` (both maps in one walk over the keys; the
-difference, the head norm and the constant in its epilogue; single tokens with long reaches in splits of the keys) and,
-from ``csrc/ssm.cu``, the update of the convolution's state record.
+difference, the head norm and the constant in its epilogue; single tokens with long reaches in splits of the keys),
+``diff_attention_mma`` (the same on tensor cores for prompt portions in bfloat16: both maps' weights meet one tile of
+values) and, from ``csrc/ssm.cu``, the update of the convolution's state record.
 """
 
 from __future__ import annotations
@@ -36,6 +37,8 @@ from .rope import rotary_frequencies
 @register_part("mixer", "diff_attention")
 class DiffAttention(Mixer):
     graph_safe = True
+    #: prompt tokens of a step from which the tensor-core kernel (tiles of 64 tokens) takes the portions
+    MMA_FROM_TOKENS = 32
 
     def __init__(self, hidden: int, n_q_heads: int, n_kv_heads: int, dim: int, v_dim: int, scale: float, diff: float,
                  eps: float, dtype: torch.dtype, device: torch.device, window: int = 0, softcap: float = 0.0, conv: int = 0,
@@ -123,15 +126,29 @@ class DiffAttention(Mixer):
         tables = ctx.block_tables[group]
         nd = ctx.n_decode
         common = dict(window=self.window, softcap=self.softcap)
+        mma = kernels.diff_mma_supported(self.dtype, self.dim, self.v_dim)
+        rep = self.n_q // self.n_kv
         if nd:
-            split, n_splits = self._decode_plan(ctx, nd * self.n_q)
+            # single tokens: a block per (sequence, kv head, split) on tensor cores, else a warp per (token, head, split)
+            split, n_splits = self._decode_plan(ctx, nd * (self.n_kv * 4 if mma else self.n_q))
             part = None
             if n_splits > 1:
                 part = ctx.buf("diff.part", (nd * self.n_q * n_splits * kernels.diff_part_floats(self.v_dim),), torch.float32)
-            kernels.diff_attention(q, k_pages, v_pages, tables, ctx.seq_of_token, ctx.positions, out, self.n_q, self.scale,
-                                   self.lam, self.eps, 1.0 - self.diff, 0, nd, split_keys=split, n_splits=n_splits, part=part,
-                                   **common)
-        if n > nd:
+            if mma:
+                rows = kernels.DIFF_MMA_TOKEN_ROWS if rep <= kernels.DIFF_MMA_TOKEN_ROWS else kernels.DIFF_MMA_ROWS
+                kernels.diff_attention_mma(q, k_pages, v_pages, tables, ctx.seq_starts, ctx.positions, out, self.n_q, self.scale,
+                                           self.lam, self.eps, 1.0 - self.diff, 0, nd, 0, nd, nd * -(-rep // rows),
+                                           split_keys=split, n_splits=n_splits, part=part, tile_rows=rows, **common)
+            else:
+                kernels.diff_attention(q, k_pages, v_pages, tables, ctx.seq_of_token, ctx.positions, out, self.n_q, self.scale,
+                                       self.lam, self.eps, 1.0 - self.diff, 0, nd, split_keys=split, n_splits=n_splits, part=part,
+                                       **common)
+        if n - nd >= self.MMA_FROM_TOKENS and mma:
+            # portions of prompts on tensor cores: blocks of 64 (token, head) rows of one sequence and one kv head
+            kernels.diff_attention_mma(q, k_pages, v_pages, tables, ctx.seq_starts, ctx.positions, out, self.n_q, self.scale,
+                                       self.lam, self.eps, 1.0 - self.diff, nd, ctx.n_seqs - nd, nd, n - nd,
+                                       kernels.diff_mma_tiles(ctx.host_q_len[nd:], rep), **common)
+        elif n > nd:
             kernels.diff_attention(q, k_pages, v_pages, tables, ctx.seq_of_token, ctx.positions, out, self.n_q, self.scale,
                                    self.lam, self.eps, 1.0 - self.diff, nd, n - nd, **common)
         y = ctx.buf("mixer.out", (n, self.hidden), self.dtype)

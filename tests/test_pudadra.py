@@ -485,7 +485,8 @@ def _diff_reference(q, keys, values, where, scale, window, cap, lam, eps, out_sc
 
 DIFF_CASES = [  # (heads, kv heads, map size, value size, page, window)
     (4, 2, 16, 24, 16, 24), (6, 1, 24, 72, 8, 17), (2, 2, 64, 128, 16, 64), (3, 3, 8, 10, 16, 9), (4, 2, 12, 25, 16, 1),
-    (4, 1, 32, 64, 32, 130), (2, 1, 48, 96, 16, 0), (8, 2, 64, 200, 64, 100),
+    (4, 1, 32, 64, 32, 130), (2, 1, 48, 96, 16, 0), (8, 2, 64, 200, 64, 100), (4, 2, 80, 40, 16, 70), (2, 2, 16, 8, 4, 33),
+    (4, 1, 128, 128, 16, 200),
 ]
 
 
@@ -552,6 +553,47 @@ def test_differential_attention_with_keys_made_dominant(case, dtype):
         k.diff_attention(qd, k_pages, v_pages, tables, seq, pos, out, H, 0.5, lam, eps, out_scale, 0, n, window=window, softcap=cap,
                          split_keys=split, n_splits=n_splits, part=part)
         assert (out.double().cpu().view(n, H, dv) - want).abs().max() < tol, f"splits of {split}"
+    if k.diff_mma_supported(tdt, d, dv):
+        # the tensor-core form takes whole portions: every sequence's last tokens as the step's rows, each looking for a key
+        new = [70, 1, (window or 50) + 2, 129]
+        g2 = torch.Generator().manual_seed(5)
+        qs, wh = [], []
+        for s_, n_ in enumerate(lens):
+            for i, p_ in enumerate(range(n_ - new[s_], n_)):
+                first = p_ - (window or 50) + 1
+                target = max(0, min(p_, [first, first - 1, p_, (p_ // page) * page - 1, (p_ // page) * page, 0, first + 1][i % 7]))
+                other_t = max(0, min(p_, 2 * first - target))
+                qq = torch.randn(H, 2, d, generator=g2, dtype=torch.float64) * 0.3
+                for h in range(H):
+                    for m_, tg in ((0, target), (1, other_t)):
+                        kk = keys[s_][tg, h // (H // G), m_]
+                        qq[h, m_] += 12.0 * kk / kk.norm() ** 2
+                qs.append(qq.to(tdt).double())
+                wh.append((s_, p_))
+        q2 = torch.stack(qs)
+        want2 = _diff_reference(q2, keys, values, wh, 0.5, window, cap, lam, eps, out_scale, H // G)
+        starts = torch.tensor([0] + list(np.cumsum(new)), dtype=torch.int32).cuda()
+        pos2 = torch.tensor([p_ for _, p_ in wh], dtype=torch.int32).cuda()
+        out2 = torch.full((len(wh), H * dv), float("nan"), dtype=tdt, device="cuda")
+        q2d = q2.reshape(len(wh), -1).to(tdt).cuda().contiguous()
+        k.diff_attention_mma(q2d, k_pages, v_pages, tables, starts, pos2, out2, H, 0.5, lam, eps, out_scale, 0, len(lens), 0, len(wh),
+                             k.diff_mma_tiles(new, H // G), window=window, softcap=cap)
+        assert (out2.double().cpu().view(len(wh), H, dv) - want2).abs().max() < tol, "tensor cores, portions"
+        # single tokens: the last token of every sequence as a step of its own, in splits of two sizes
+        last = [int(starts[i + 1]) - 1 for i in range(len(lens))]
+        q1, pos1 = q2d[last].contiguous(), pos2[last].contiguous()
+        starts1 = torch.arange(len(lens) + 1, dtype=torch.int32).cuda()
+        for split in (64, 128):
+            n_splits = -(-max(lens) // split) if not window else min(-(-max(lens) // split), (window - 1) // split + 2)
+            part = torch.full((len(last) * H * n_splits * k.diff_part_floats(dv),), float("nan"), dtype=torch.float32, device="cuda")
+            out1 = torch.full((len(last), H * dv), float("nan"), dtype=tdt, device="cuda")
+            for rows in (16, 64):
+                out1.fill_(float("nan"))
+                k.diff_attention_mma(q1, k_pages, v_pages, tables, starts1, pos1, out1, H, 0.5, lam, eps, out_scale, 0, len(lens), 0,
+                                     len(last), k.diff_mma_tiles([1] * len(last), H // G, rows), window=window, softcap=cap,
+                                     split_keys=split, n_splits=n_splits, part=part if n_splits > 1 else None, tile_rows=rows)
+                assert (out1.double().cpu().view(len(last), H, dv) - want2[last]).abs().max() < tol, \
+                    f"tensor cores, single tokens, splits of {split}, tiles of {rows} rows"
     # a range of rows in the middle of the batch leaves the others alone
     out.fill_(7.0)
     k.diff_attention(qd, k_pages, v_pages, tables, seq, pos, out, H, 0.5, lam, eps, out_scale, 5, n - 9, window=window, softcap=cap)
