@@ -835,7 +835,7 @@ def run_pudadra(args, measure, n_layers: int, block: int, clocks, peak_source: s
     out: dict = {}
     for name, size in DESIGN_SIZES.items():
         out[name] = {"layers": n_layers, "pudadra": measure(pudadra_config(size, n_layers), size["vocab"]),
-                     "vokusun": measure(vokusun_config(size, min(n_layers, 4)), size["vocab"])}
+                     "vokusun": measure(vokusun_config(size, n_layers), size["vocab"])}
     size = DESIGN_SIZES["w2048"]
     att, win = size["att"], PUDADRA_WINDOW
     ns = lambda **kw: types.SimpleNamespace(dtype="bfloat16", iters=10, warmup=3, page=block, sequential_pages=False, **kw)  # noqa: E731

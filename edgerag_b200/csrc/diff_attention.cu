@@ -40,12 +40,16 @@ __device__ __forceinline__ float2 load_pair(const __nv_bfloat16* p) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// prepare: one block per token.  Row layout of `proj`: H heads of [map 1 | map 2] queries (dim each), G heads of
-// [map 1 | map 2] keys, G heads of values (vdim).  conv_w: float [channels][taps] in that order, or null.
-// conv_state: float [slots][taps - 1][channels], oldest first.
+// prepare.  Row layout of `proj`: H heads of [map 1 | map 2] queries (dim each), G heads of [map 1 | map 2] keys, G heads
+// of values (vdim).  conv_w: float [channels][taps] in that order, or null.  conv_state: float [slots][taps - 1][channels],
+// oldest first.  A "unit" is one map of a q or k head, or one value head: a warp takes a unit at a time (convolution into
+// its strip of shared memory, then rotation and store), so nothing waits on the block; the block's cosines and sines of
+// position * inv_freq are made once.  grid (tokens, blocks that share a token's units).
 // ---------------------------------------------------------------------------------------------
+constexpr int kPrepWarps = 8;
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kPrepWarps * 32)
 diff_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w, int taps,
                     const float* __restrict__ conv_state, const int* __restrict__ seq_of_token,
                     const int* __restrict__ seq_starts, const int* __restrict__ state_slots, const int* __restrict__ positions,
@@ -53,54 +57,66 @@ diff_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restrict_
                     T* __restrict__ q_out, const int* __restrict__ slots, T* __restrict__ k_pages, T* __restrict__ v_pages,
                     int page_size) {
   chain_wait();
-  extern __shared__ float row_s[];                 // the token's q, k and v after the convolution
-  const int t = blockIdx.x;
-  const int qw = H * 2 * dim, kw = G * 2 * dim, channels = qw + kw + G * vdim;
-  const T* row = proj + (size_t)t * ld;
-  if (conv_w && taps > 1) {
-    const int seq = seq_of_token[t], start = seq_starts[seq], i = t - start;
-    const float* old = conv_state + (size_t)state_slots[seq] * (taps - 1) * channels;
-    for (int ch = threadIdx.x; ch < channels; ch += blockDim.x) {
-      float acc = 0.f;
-      for (int j = 0; j < taps; ++j) {
-        const int r = i - (taps - 1 - j);          // index inside the portion of the input under tap j
-        const float u = r >= 0 ? Elem<T>::load(proj + (size_t)(start + r) * ld + ch) : old[(size_t)(taps - 1 + r) * channels + ch];
-        acc = fmaf(conv_w[(size_t)ch * taps + j], u, acc);
-      }
-      row_s[ch] = acc;
-    }
-  } else {
-    for (int ch = threadIdx.x; ch < channels; ch += blockDim.x) row_s[ch] = (conv_w ? conv_w[ch] : 1.f) * Elem<T>::load(row + ch);
-  }
-  __syncthreads();
+  extern __shared__ float prep_s[];                // [rot_dims] cosines then sines, then a strip of max(dim, vdim) per warp
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int half = rot_dims / 2, wide = dim > vdim ? dim : vdim;
+  float* cs_s = prep_s;
+  float* sn_s = prep_s + half;
+  float* strip = prep_s + rot_dims + warp * wide;
   const float pos = (float)positions[t];
-  const int half = rot_dims / 2;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &sn_s[j], &cs_s[j]);
+  __syncthreads();
+  const int qw = H * 2 * dim, kw = G * 2 * dim, channels = qw + kw + G * vdim;
+  const int n_maps = 2 * (H + G), n_units = n_maps + G;
+  const bool conv = conv_w && taps > 1;
+  int start = 0, i = 0;
+  const float* old = nullptr;
+  if (conv) {
+    const int seq = seq_of_token[t];
+    start = seq_starts[seq];
+    i = t - start;                                 // index of the token inside its portion
+    old = conv_state + (size_t)state_slots[seq] * (taps - 1) * channels;
+  }
   const int slot = slots ? slots[t] : -1;
   const int page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot % page_size : 0;
-  // queries and keys: maps of `dim` entries, the first rot_dims of each turned in halves
-  const int n_maps = 2 * (H + G);
-  for (int idx = threadIdx.x; idx < n_maps * dim; idx += blockDim.x) {
-    const int map = idx / dim, e = idx % dim;
-    const float* m = row_s + map * dim;
-    float v = m[e];
-    if (e < rot_dims) {
-      const int j = e < half ? e : e - half;
-      float sn, cs;
-      sincosf(pos * inv_freq[j], &sn, &cs);
-      v = e < half ? m[e] * cs - m[e + half] * sn : m[e] * cs + m[e - half] * sn;
+  for (int u = blockIdx.y * kPrepWarps + warp; u < n_units; u += gridDim.y * kPrepWarps) {
+    const bool is_map = u < n_maps;
+    const int width = is_map ? dim : vdim;
+    const int ch0 = is_map ? u * dim : n_maps * dim + (u - n_maps) * vdim;
+    if (!is_map && slot < 0) continue;             // (values only go to the cache)
+    for (int e = lane; e < width; e += 32) {
+      const int ch = ch0 + e;
+      float acc;
+      if (conv) {
+        acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+          const int r = i - (taps - 1 - j);        // index inside the portion of the input under tap j
+          const float x = r >= 0 ? Elem<T>::load(proj + (size_t)(start + r) * ld + ch) : old[(size_t)(taps - 1 + r) * channels + ch];
+          acc = fmaf(conv_w[(size_t)ch * taps + j], x, acc);
+        }
+      } else {
+        acc = (conv_w ? conv_w[ch] : 1.f) * Elem<T>::load(proj + (size_t)t * ld + ch);
+      }
+      strip[e] = acc;
     }
-    if (map < 2 * H) {
-      Elem<T>::store(q_out + (size_t)t * qw + idx, v);
-    } else if (slot >= 0) {
-      const int kk = idx - qw, g = kk / (2 * dim), ee = kk % (2 * dim);
-      Elem<T>::store(k_pages + (((size_t)page * G + g) * page_size + offset) * (2 * dim) + ee, v);
+    __syncwarp();
+    if (is_map) {
+      const bool is_q = u < 2 * H;
+      T* dst = is_q ? q_out + (size_t)t * qw + ch0
+                    : k_pages + (((size_t)page * G + (u - 2 * H) / 2) * page_size + offset) * (2 * dim) + ((u - 2 * H) & 1) * dim;
+      if (is_q || slot >= 0) {
+        for (int e = lane; e < dim; e += 32) {
+          float v = strip[e];
+          if (e < half) v = strip[e] * cs_s[e] - strip[e + half] * sn_s[e];
+          else if (e < rot_dims) v = strip[e] * cs_s[e - half] + strip[e - half] * sn_s[e - half];
+          Elem<T>::store(dst + e, v);
+        }
+      }
+    } else {
+      T* dst = v_pages + (((size_t)page * G + (u - n_maps)) * page_size + offset) * vdim;
+      for (int e = lane; e < vdim; e += 32) Elem<T>::store(dst + e, strip[e]);
     }
-  }
-  if (slot >= 0) {
-    for (int idx = threadIdx.x; idx < G * vdim; idx += blockDim.x) {
-      const int g = idx / vdim, e = idx % vdim;
-      Elem<T>::store(v_pages + (((size_t)page * G + g) * page_size + offset) * vdim + e, row_s[qw + kw + idx]);
-    }
+    __syncwarp();
   }
 }
 
@@ -581,6 +597,7 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     for (int mp = 0; mp < 2; ++mp)
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
+        if (g + 8 * r >= valid) continue;
         float* dst = M + ((size_t)(warp * 2 + mp) * 16 + g + 8 * r) * mst;
 #pragma unroll
         for (int nt = 0; nt < 2 * VT; ++nt) {
@@ -761,14 +778,17 @@ ERB_EXPORT int erb_diff_prepare(const void* proj, int n_tokens, int ld, const fl
     return fail(ERB_ERR_ARG, "diff_prepare: bad sizes (rot_dims %d of dim %d, %d taps)", rot_dims, dim, taps);
   const int channels = (H + G) * 2 * dim + G * vdim;
   if (ld < channels) return fail(ERB_ERR_ARG, "diff_prepare: rows too narrow");
-  const size_t smem = sizeof(float) * channels;
-  if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "diff_prepare: rows of %d channels", channels);
+  const size_t smem = sizeof(float) * ((size_t)rot_dims + (size_t)kPrepWarps * (dim > vdim ? dim : vdim));
+  if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "diff_prepare: maps of %d and values of %d entries", dim, vdim);
+  // few tokens: a token's units are spread over several blocks
+  const int n_units = 2 * (H + G) + G;
+  const int share = n_tokens >= 256 ? 1 : (n_units + kPrepWarps - 1) / kPrepWarps;
   auto kern = diff_prepare_kernel<elem_t>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "diff_prepare: %s", cudaGetErrorString(e));
   }
-  launch_chained(kern, dim3(n_tokens), dim3(256), smem, (cudaStream_t)stream, (const elem_t*)proj, ld, conv_w, taps, conv_state,
+  launch_chained(kern, dim3(n_tokens, share), dim3(kPrepWarps * 32), smem, (cudaStream_t)stream, (const elem_t*)proj, ld, conv_w, taps, conv_state,
                  seq_of_token, seq_starts, state_slots, positions, inv_freq, rot_dims, H, G, dim, vdim, (elem_t*)q_out, slots,
                  (elem_t*)k_pages, (elem_t*)v_pages, page_size);
   return check_launch("diff_prepare");
