@@ -434,18 +434,20 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     __nv_bfloat16* kd = Ks + stage * kMmaKeys * kst;
     __nv_bfloat16* vd = Vs + stage * kMmaKeys * vst;
     const int my_key = k0 + warp + kMmaWarps * (lane & 15);
-    long long my_row = -1;                                       // (page * G + kv head) * page_size + offset, or -1 past the end
-    if (my_key < end) my_row = ((long long)bt[my_key / page_size] * G + kvh) * page_size + my_key % page_size;
+    int my_row = -1;                                             // (page * G + kv head) * page_size + offset, or -1 past the end
+    if (my_key < end) my_row = (bt[my_key / page_size] * G + kvh) * page_size + my_key % page_size;
+    for (int c0 = 0; c0 < kv_chunks; c0 += 32) {                 // (one turn where a row of keys and values has 32 pieces at most)
+      const int c = c0 + lane;
+      const bool mine = c < kv_chunks, is_k = c < q_chunks;     // (every lane takes part in the shuffles below)
+      const int cc = is_k ? c : (mine ? c - q_chunks : 0);
+      const __nv_bfloat16* src = (is_k ? k_pages : v_pages) + 8 * cc;
+      const size_t src_ld = is_k ? kw : vdim;
+      __nv_bfloat16* dst = (is_k ? kd : vd) + 8 * cc + warp * (is_k ? kst : vst);
+      const int dst_ld = kMmaWarps * (is_k ? kst : vst);
 #pragma unroll 4
-    for (int j = 0; j < kMmaKeys / kMmaWarps; ++j) {
-      const long long row = __shfl_sync(0xffffffffu, my_row, j);
-      const bool real = row >= 0;
-      const int r = warp + kMmaWarps * j;
-      const __nv_bfloat16* ksrc = k_pages + (real ? row : 0) * kw;
-      const __nv_bfloat16* vsrc = v_pages + (real ? row : 0) * vdim;
-      for (int c = lane; c < kv_chunks; c += 32) {
-        if (c < q_chunks) copy16(kd + r * kst + 8 * c, ksrc + 8 * c, real);
-        else copy16(vd + r * vst + 8 * (c - q_chunks), vsrc + 8 * (c - q_chunks), real);
+      for (int j = 0; j < kMmaKeys / kMmaWarps; ++j) {
+        const int row = __shfl_sync(0xffffffffu, my_row, j);
+        if (mine) copy16(dst + j * dst_ld, src + (row >= 0 ? row : 0) * src_ld, row >= 0);
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -458,7 +460,6 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
   const int w_last = min(valid - 1, row0_w + 15);
   const int w_pos_max = row0_w < valid ? positions[token_of(w_last)] : -1, w_pos_min = row0_w < valid ? positions[token_of(row0_w)] : -1;
   const int w_low_min = first_visible_key(w_pos_min, window), w_low_max = first_visible_key(w_pos_max, window);
-  const bool w_full = row0_w + 15 < valid;                          // (rows past the valid ones must stay masked)
   const float cap2 = cap > 0.f ? 2.f / cap : 0.f;
   float m[2][2], l[2][2];                                           // [map][row]: running maximum, this thread's share of the sum
   float o[2][2 * VT][4];
@@ -488,7 +489,8 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     const int kf = k0 + key0_w, kl = kf + 8 * NTW - 1;              // the first and last key this warp looks at in the tile
     // (a warp whose rows all lie before its first key, or whose windows all lie behind its last, has nothing here)
     const bool idle = row0_w >= valid || kf > w_pos_max || kl < w_low_min || kf >= end;
-    const bool plain = w_full && kf >= w_low_max && kl <= w_pos_min && kl < end;      // no key of it is masked for any row
+    // no key of it is masked for any valid row (rows past the valid ones hold queries of zeros and are never stored)
+    const bool plain = kf >= w_low_max && kl <= w_pos_min && kl < end;
     if (!idle) {
 #pragma unroll
       for (int mp = 0; mp < 2; ++mp) {
@@ -558,10 +560,12 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
           pa[nt >> 1][2 * (nt & 1)] = pack_bf16(p[0], p[1]);
           pa[nt >> 1][2 * (nt & 1) + 1] = pack_bf16(p[2], p[3]);
         }
+        if (alpha[0] != 1.f || alpha[1] != 1.f) {       // (a tile that raised neither row's maximum rescales nothing)
 #pragma unroll
-        for (int nt = 0; nt < 2 * VT; ++nt) {
-          o[mp][nt][0] *= alpha[0]; o[mp][nt][1] *= alpha[0];
-          o[mp][nt][2] *= alpha[1]; o[mp][nt][3] *= alpha[1];
+          for (int nt = 0; nt < 2 * VT; ++nt) {
+            o[mp][nt][0] *= alpha[0]; o[mp][nt][1] *= alpha[0];
+            o[mp][nt][2] *= alpha[1]; o[mp][nt][3] *= alpha[1];
+          }
         }
 #pragma unroll
         for (int ks = 0; ks < NTW / 2; ++ks) {
