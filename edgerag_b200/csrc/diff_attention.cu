@@ -712,6 +712,263 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
   }
 }
 
+// Single tokens whose kv head serves at most 8 query heads: both maps in ONE tile of 16 rows.  Row r < 8 holds head r's
+// first map as [q1 | 0], row 8 + r its second map as [0 | q2], so one product over the whole key row [k1 | k2] gives both
+// maps' scores, one softmax state a row serves both, and one accumulator holds a1 in rows 0 .. 7 and a2 in rows 8 .. 15: half
+// the registers, products and exponentials of the two-pass form.  The four warps share out a tile's keys; their states are
+// merged through shared memory; splits over grid z.  One block per (sequence, kv head, split).
+template <int VT>
+__global__ void __launch_bounds__(kMmaWarps * 32, 3)
+diff_attention_mma_packed_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+                                 const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_tables, int max_pages,
+                                 const int* __restrict__ seq_starts, const int* __restrict__ positions,
+                                 __nv_bfloat16* __restrict__ out, float* __restrict__ part, int first_token, int seq0, int H, int G,
+                                 int dim, int vdim, int page_size, int window, int split_keys, int n_splits, float scale, float cap,
+                                 float lambda, float eps, float out_scale) {
+  chain_wait();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int kw = 2 * dim, kst = kw + 8, vst = 16 * VT + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][kst]
+  __nv_bfloat16* Ks = Qs + 16 * kst;                               // [2][64][kst]
+  __nv_bfloat16* Vs = Ks + 2 * kMmaKeys * kst;                     // [2][64][vst]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int s = seq0 + blockIdx.x, kvh = blockIdx.y, rep = H / G, split = blockIdx.z;
+  const int tok = seq_starts[s], pos = positions[tok];
+  const int lo = first_visible_key(pos, window);
+  const int base = n_splits > 1 ? (lo / split_keys + split) * split_keys : 0;
+  const int begin = n_splits > 1 ? max(lo, base) : lo;
+  const int end = n_splits > 1 ? min(pos + 1, base + split_keys) : pos + 1;
+  const int* bt = block_tables + (size_t)s * max_pages;
+  const int key0_w = 16 * warp;
+
+  const int q_chunks = kw / 8, half_chunks = dim / 8;
+  for (int idx = threadIdx.x; idx < 16 * q_chunks; idx += blockDim.x) {
+    const int r = idx / q_chunks, c = idx % q_chunks;
+    const int head = r & 7, second = r >> 3;                       // rows 0 .. 7: first maps, 8 .. 15: second maps
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (head < rep && (c >= half_chunks) == (second != 0))
+      v = *reinterpret_cast<const uint4*>(q + ((size_t)tok * H + kvh * rep + head) * kw + 8 * c);
+    *reinterpret_cast<uint4*>(Qs + r * kst + 8 * c) = v;
+  }
+  if (16 * VT > vdim) {
+    const int extra = 16 * VT - vdim;
+    for (int idx = threadIdx.x; idx < 2 * kMmaKeys * extra; idx += blockDim.x)
+      Vs[(idx / extra) * vst + vdim + idx % extra] = __float2bfloat16_rn(0.f);
+  }
+  const int v_chunks = vdim / 8, kv_chunks = q_chunks + v_chunks;
+  auto load_tile = [&](int k0, int stage) {
+    __nv_bfloat16* kd = Ks + stage * kMmaKeys * kst;
+    __nv_bfloat16* vd = Vs + stage * kMmaKeys * vst;
+    const int my_key = k0 + warp + kMmaWarps * (lane & 15);
+    int my_row = -1;
+    if (my_key < end) my_row = (bt[my_key / page_size] * G + kvh) * page_size + my_key % page_size;
+    for (int c0 = 0; c0 < kv_chunks; c0 += 32) {
+      const int c = c0 + lane;
+      const bool mine = c < kv_chunks, is_k = c < q_chunks;
+      const int cc = is_k ? c : (mine ? c - q_chunks : 0);
+      const __nv_bfloat16* src = (is_k ? k_pages : v_pages) + 8 * cc;
+      const size_t src_ld = is_k ? kw : vdim;
+      __nv_bfloat16* dst = (is_k ? kd : vd) + 8 * cc + warp * (is_k ? kst : vst);
+      const int dst_ld = kMmaWarps * (is_k ? kst : vst);
+#pragma unroll 4
+      for (int j = 0; j < kMmaKeys / kMmaWarps; ++j) {
+        const int row = __shfl_sync(0xffffffffu, my_row, j);
+        if (mine) copy16(dst + j * dst_ld, src + (row >= 0 ? row : 0) * src_ld, row >= 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  const float cap2 = cap > 0.f ? 2.f / cap : 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};          // rows g (a first map) and g + 8 (a second map)
+  float o[2 * VT][4];
+#pragma unroll
+  for (int nt = 0; nt < 2 * VT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[nt][i] = 0.f;
+
+  const int n_tiles = begin < end ? (end - begin + kMmaKeys - 1) / kMmaKeys : 0;
+  if (n_tiles > 0) load_tile(begin, 0);
+  for (int it = 0; it < n_tiles; ++it) {
+    const int k0 = begin + it * kMmaKeys, stage = it & 1;
+    if (it + 1 < n_tiles) {
+      load_tile(k0 + kMmaKeys, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const __nv_bfloat16* Kt = Ks + stage * kMmaKeys * kst;
+    const __nv_bfloat16* Vt = Vs + stage * kMmaKeys * vst;
+    const int kf = k0 + key0_w, kl = kf + 15;
+    if (kf < end) {                                                // (keys begin .. end - 1 are all inside the window and not after the token)
+      float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const __nv_bfloat16* qa = Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kst + 8 * (lane >> 4);
+      const __nv_bfloat16* kb = Kt + (key0_w + (lane & 7) + 8 * (lane >> 4)) * kst + 8 * ((lane >> 3) & 1);
+      for (int kk = 0; kk < kw; kk += 16) {
+        uint32_t a[4], b[4];
+        ldsm4(a, qa + kk);
+        ldsm4(b, kb + kk);
+        mma16816(sc[0], a, b[0], b[1]);
+        mma16816(sc[1], a, b[2], b[3]);
+      }
+      float top[2] = {m[0], m[1]};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float v = soft_cap_fast(sc[nt][i] * scale, cap, cap2);
+          if (kl >= end && kf + 8 * nt + 2 * tq + (i & 1) >= end) v = -INFINITY;
+          sc[nt][i] = v;
+          top[i >> 1] = fmaxf(top[i >> 1], v);
+        }
+      float alpha[2], shift[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 1));
+        top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 2));
+        alpha[r] = m[r] == -INFINITY ? 0.f : __expf(m[r] - top[r]);
+        shift[r] = top[r];                                          // (finite: the warp has at least one key here)
+        m[r] = top[r];
+        l[r] *= alpha[r];
+      }
+      uint32_t pa[4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        float p[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          p[i] = __expf(sc[nt][i] - shift[i >> 1]);
+          l[i >> 1] += p[i];
+        }
+        pa[2 * nt] = pack_bf16(p[0], p[1]);
+        pa[2 * nt + 1] = pack_bf16(p[2], p[3]);
+      }
+      if (alpha[0] != 1.f || alpha[1] != 1.f) {
+#pragma unroll
+        for (int nt = 0; nt < 2 * VT; ++nt) {
+          o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
+          o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+        }
+      }
+#pragma unroll
+      for (int pr = 0; pr < VT; ++pr) {
+        uint32_t b[4];
+        ldsm4t(b, Vt + (key0_w + (lane & 7) + 8 * ((lane >> 3) & 1)) * vst + 16 * pr + 8 * (lane >> 4));
+        mma16816(o[2 * pr], pa, b[0], b[1]);
+        mma16816(o[2 * pr + 1], pa, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  // the warps' states to shared memory (over the stages), float [warp][row 16][16 VT + 2]; then warp w finishes heads w, w + 4
+  const int mst = 16 * VT + 2;
+  float* M = reinterpret_cast<float*>(smem_raw);
+  __syncthreads();
+  if (g < rep) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float* dst = M + ((size_t)warp * 16 + g + 8 * r) * mst;
+#pragma unroll
+      for (int nt = 0; nt < 2 * VT; ++nt) {
+        dst[8 * nt + 2 * tq] = o[nt][2 * r];
+        dst[8 * nt + 2 * tq + 1] = o[nt][2 * r + 1];
+      }
+      if (tq == 0) { dst[16 * VT] = m[r]; dst[16 * VT + 1] = l[r]; }
+    }
+  }
+  __syncthreads();
+  const int vpad = 64 * (vdim <= 64 ? 1 : (vdim <= 128 ? 2 : 4));
+  for (int head = warp; head < rep; head += kMmaWarps) {
+    float wgt[2][kMmaWarps], top[2], sum[2];
+#pragma unroll
+    for (int mp = 0; mp < 2; ++mp) {
+      const int row = head + 8 * mp;
+      top[mp] = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) top[mp] = fmaxf(top[mp], M[((size_t)w * 16 + row) * mst + 16 * VT]);
+      sum[mp] = 0.f;
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) {
+        const float* src = M + ((size_t)w * 16 + row) * mst + 16 * VT;
+        wgt[mp][w] = src[0] == -INFINITY ? 0.f : __expf(src[0] - top[mp]);
+        sum[mp] = fmaf(src[1], wgt[mp][w], sum[mp]);
+      }
+    }
+    float acc[2][(16 * VT + 31) / 32];
+#pragma unroll
+    for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+      for (int i = 0; i < (16 * VT + 31) / 32; ++i) {
+        const int c = lane + 32 * i;
+        float v = 0.f;
+        if (c < 16 * VT) {
+#pragma unroll
+          for (int w = 0; w < kMmaWarps; ++w) v = fmaf(M[((size_t)w * 16 + head + 8 * mp) * mst + c], wgt[mp][w], v);
+        }
+        acc[mp][i] = v;
+      }
+    const int qh = kvh * rep + head;
+    if (n_splits > 1) {
+      float* dst = part + ((size_t)((tok - first_token) * H + qh) * n_splits + split) * (4 + 2 * vpad);
+      if (lane == 0) { dst[0] = top[0]; dst[1] = sum[0]; dst[2] = top[1]; dst[3] = sum[1]; }
+#pragma unroll
+      for (int i = 0; i < (16 * VT + 31) / 32; ++i) {
+        const int c = lane + 32 * i;
+        if (c < vdim) { dst[4 + c] = acc[0][i]; dst[4 + vpad + c] = acc[1][i]; }
+      }
+      continue;
+    }
+    const float r1 = 1.f / sum[0], r2 = lambda / sum[1];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < (16 * VT + 31) / 32; ++i) {
+      acc[0][i] = acc[0][i] * r1 - acc[1][i] * r2;
+      if (lane + 32 * i < vdim) ss = fmaf(acc[0][i], acc[0][i], ss);
+    }
+    const float f = rsqrtf(warp_sum(ss) / (float)vdim + eps) * out_scale;
+    __nv_bfloat16* dst = out + ((size_t)tok * H + qh) * vdim;
+#pragma unroll
+    for (int i = 0; i < (16 * VT + 31) / 32; ++i) {
+      const int c = lane + 32 * i;
+      if (c < vdim) dst[c] = __float2bfloat16_rn(acc[0][i] * f);
+    }
+  }
+}
+
+template <int VT>
+int launch_mma_packed(cudaStream_t st, const void* q, const void* k_pages, const void* v_pages, const int* block_tables,
+                      int max_pages, const int* seq_starts, const int* positions, void* out, float* part, int first_token,
+                      int n_tokens, int seq0, int n_seqs, int H, int G, int dim, int vdim, int page_size, int window, int split_keys,
+                      int n_splits, float scale, float cap, float lambda, float eps, float out_scale) {
+  size_t smem = sizeof(__nv_bfloat16) * ((size_t)(16 + 2 * kMmaKeys) * (2 * dim + 8) + 2 * (size_t)kMmaKeys * (16 * VT + 8));
+  smem = std::max(smem, sizeof(float) * kMmaWarps * 16 * (size_t)(16 * VT + 2));
+  auto kern = diff_attention_mma_packed_kernel<VT>;
+  if (smem > 227 * 1024) return fail(ERB_ERR_UNSUPPORTED, "diff_attention_mma: maps of %d entries need %zu bytes of shared memory", dim, smem);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "diff_attention_mma: %s", cudaGetErrorString(e));
+  }
+  launch_chained(kern, dim3(n_seqs, G, n_splits), dim3(kMmaWarps * 32), smem, st, (const __nv_bfloat16*)q,
+                 (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_tables, max_pages, seq_starts, positions,
+                 (__nv_bfloat16*)out, part, first_token, seq0, H, G, dim, vdim, page_size, window, split_keys, n_splits, scale, cap,
+                 lambda, eps, out_scale);
+  int rc = check_launch("diff_attention_mma");
+  if (rc || n_splits == 1) return rc;
+  const int n_rows = n_tokens * H;
+  auto merge = [&](auto kernel) {
+    launch_chained(kernel, dim3((n_rows + kWarps - 1) / kWarps), dim3(kWarps * 32), 0, st, (const float*)part, (__nv_bfloat16*)out,
+                   first_token, n_rows, H, vdim, n_splits, lambda, eps, out_scale);
+  };
+  if (vdim <= 64) merge(diff_combine_kernel<__nv_bfloat16, 1>); else merge(diff_combine_kernel<__nv_bfloat16, 2>);
+  return check_launch("diff_combine");
+}
+
 template <int VT, bool DEC>
 int launch_mma(cudaStream_t st, const void* q, const void* k_pages, const void* v_pages, const int* block_tables, int max_pages,
                const int* seq_starts, const int* positions, void* out, float* part, int first_token, int n_tokens, int seq0,
@@ -822,7 +1079,8 @@ ERB_EXPORT int erb_diff_attention(const void* q, const void* k_pages, const void
 
 // The tensor-core form (bfloat16 build only): sequences seq0 .. seq0 + n_seqs of the batch, whose rows are tokens
 // seq_starts[s] .. seq_starts[s + 1] (tokens first_token .. first_token + n_tokens in all); `n_tiles` = sum over them of
-// ceil(tokens * (H / G) / tile_rows), tile_rows 64 (portions) or 16 (single tokens: the warps share out a tile's keys).  With n_splits > 1 (single tokens) `part` takes the splits' states as for erb_diff_attention.
+// ceil(tokens * (H / G) / tile_rows), tile_rows 64 (portions) or 16 (single tokens: the warps share out a tile's keys);
+// tile_rows 8: single tokens (one per sequence) with at most 8 heads a kv head, both maps packed into one tile of 16 rows.  With n_splits > 1 (single tokens) `part` takes the splits' states as for erb_diff_attention.
 // Needs maps of a multiple of 16 entries and value rows of a multiple of 8 entries, at most 128.
 ERB_EXPORT int erb_diff_attention_mma(const void* q, const void* k_pages, const void* v_pages, const int* block_tables,
                                       int max_pages, const int* seq_starts, const int* positions, void* out, float* part,
@@ -833,10 +1091,13 @@ ERB_EXPORT int erb_diff_attention_mma(const void* q, const void* k_pages, const 
   if (n_seqs <= 0 || n_tiles <= 0) return ERB_OK;
   if (H <= 0 || G <= 0 || H % G || dim <= 0 || dim % 16 || vdim <= 0 || vdim % 8 || vdim > 128 || page_size <= 0 || window < 0 ||
       ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || ((uintptr_t)out & 3) || n_splits < 1 ||
-      (n_splits > 1 && (!part || split_keys <= 0 || ((uintptr_t)part & 7))) || (tile_rows != 16 && tile_rows != 64))
+      (n_splits > 1 && (!part || split_keys <= 0 || ((uintptr_t)part & 7))) || (tile_rows != 8 && tile_rows != 16 && tile_rows != 64) ||
+      (tile_rows == 8 && (H / G > 8 || n_tiles != n_seqs || n_tokens != n_seqs)))
     return fail(ERB_ERR_UNSUPPORTED, "diff_attention_mma: sizes (maps of %d, values of %d) or alignment not supported", dim, vdim);
   cudaStream_t st = (cudaStream_t)stream;
-#define ERB_DIFF_MMA(VT) (tile_rows == 16 ? ERB_DIFF_MMA2(VT, true) : ERB_DIFF_MMA2(VT, false))
+#define ERB_DIFF_MMA(VT) (tile_rows == 8 ? launch_mma_packed<VT>(st, q, k_pages, v_pages, block_tables, max_pages, seq_starts, positions, \
+    out, part, first_token, n_tokens, seq0, n_seqs, H, G, dim, vdim, page_size, window, split_keys, n_splits, scale, cap, lambda, eps,   \
+    out_scale) : tile_rows == 16 ? ERB_DIFF_MMA2(VT, true) : ERB_DIFF_MMA2(VT, false))
 #define ERB_DIFF_MMA2(VT, DEC) launch_mma<VT, DEC>(st, q, k_pages, v_pages, block_tables, max_pages, seq_starts, positions, out, part,         \
     first_token, n_tokens, seq0, n_seqs, n_tiles, H, G, dim, vdim, page_size, window, split_keys, n_splits, scale, cap, lambda, eps, \
     out_scale)

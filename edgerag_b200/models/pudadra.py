@@ -175,4 +175,6 @@ def pudadra_plan(cfg: PudadraConfig) -> ModelPlan:
         head=PartSpec("linear", {"vocab": cfg.vocab_size, "hidden": h, "tensor": "head", "tied_to": "embed",
                                  "scale": cfg.logit_scale}),
         name_prefixes=("",),
+        # (a layer without a feed-forward has no use for a second norm: a file that stores one all the same still loads)
+        ignored_prefixes=tuple(f"l{i}.norm2" for i, layer in enumerate(cfg.layers) if layer["mlp"] is None),
     )

@@ -1080,6 +1080,7 @@ def diff_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
 
 DIFF_MMA_ROWS = 64         # (token, head) rows of one sequence and kv head that a block of the tensor-core form owns
 DIFF_MMA_TOKEN_ROWS = 16   # the same for single tokens: the block's warps share out the keys instead of the rows
+DIFF_MMA_PACKED_ROWS = 8   # single tokens with at most 8 heads a kv head: both maps of a head in one tile of 16 rows
 
 
 def diff_mma_supported(dtype: torch.dtype, dim: int, v_dim: int) -> bool:
@@ -1104,7 +1105,8 @@ def diff_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Te
     rows ``first_token .. first_token + n_tokens``, sequence ``s`` owning ``seq_starts[s] .. seq_starts[s + 1]`` and row
     ``s`` of ``block_tables``); ``n_tiles = diff_mma_tiles(new tokens per sequence, heads per kv head, tile_rows)``.
     ``tile_rows`` 64: a block's warps share out the rows (portions); 16: they share out the keys (single tokens with at
-    most 16 heads per kv head).  Splits as for ``diff_attention`` (single tokens)."""
+    most 16 heads per kv head); 8: single tokens, one a sequence, with at most 8 heads per kv head, whose two maps share
+    one tile of 16 rows (half the arithmetic of the form before).  Splits as for ``diff_attention`` (single tokens)."""
     _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", torch.bfloat16); _need(v_pages, "v_pages", torch.bfloat16)
     _need(out, "out", torch.bfloat16); _need(block_tables, "block_tables", torch.int32); _need(seq_starts, "seq_starts", torch.int32)
     _need(positions, "positions", torch.int32)

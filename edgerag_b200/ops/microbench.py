@@ -431,7 +431,7 @@ def diff_attention(a) -> dict:
     mma = getattr(a, "kernel", "mma") == "mma" and kernels.diff_mma_supported(dtype, d, dv)
     if mma:
         q_lens = [1] * n if decode else [a.tokens]
-        tile_rows = 16 if (decode and H // G <= 16) else 64
+        tile_rows = (8 if H // G <= 8 else 16 if H // G <= 16 else 64) if decode else 64
         tiles = kernels.diff_mma_tiles(q_lens, H // G, tile_rows)
         starts = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
         if decode and not a.split:      # as the mixer plans: a block per (sequence, kv head, split)

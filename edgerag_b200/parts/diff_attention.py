@@ -135,7 +135,8 @@ class DiffAttention(Mixer):
             if n_splits > 1:
                 part = ctx.buf("diff.part", (nd * self.n_q * n_splits * kernels.diff_part_floats(self.v_dim),), torch.float32)
             if mma:
-                rows = kernels.DIFF_MMA_TOKEN_ROWS if rep <= kernels.DIFF_MMA_TOKEN_ROWS else kernels.DIFF_MMA_ROWS
+                rows = (kernels.DIFF_MMA_PACKED_ROWS if rep <= kernels.DIFF_MMA_PACKED_ROWS else
+                        kernels.DIFF_MMA_TOKEN_ROWS if rep <= kernels.DIFF_MMA_TOKEN_ROWS else kernels.DIFF_MMA_ROWS)
                 kernels.diff_attention_mma(q, k_pages, v_pages, tables, ctx.seq_starts, ctx.positions, out, self.n_q, self.scale,
                                            self.lam, self.eps, 1.0 - self.diff, 0, nd, 0, nd, nd * -(-rep // rows),
                                            split_keys=split, n_splits=n_splits, part=part, tile_rows=rows, **common)

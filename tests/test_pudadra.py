@@ -486,7 +486,7 @@ def _diff_reference(q, keys, values, where, scale, window, cap, lam, eps, out_sc
 DIFF_CASES = [  # (heads, kv heads, map size, value size, page, window)
     (4, 2, 16, 24, 16, 24), (6, 1, 24, 72, 8, 17), (2, 2, 64, 128, 16, 64), (3, 3, 8, 10, 16, 9), (4, 2, 12, 25, 16, 1),
     (4, 1, 32, 64, 32, 130), (2, 1, 48, 96, 16, 0), (8, 2, 64, 200, 64, 100), (4, 2, 80, 40, 16, 70), (2, 2, 16, 8, 4, 33),
-    (4, 1, 128, 128, 16, 200),
+    (4, 1, 128, 128, 16, 200), (12, 1, 16, 32, 16, 40), (24, 1, 16, 16, 16, 30), (8, 1, 32, 64, 16, 90),
 ]
 
 
@@ -587,7 +587,7 @@ def test_differential_attention_with_keys_made_dominant(case, dtype):
             n_splits = -(-max(lens) // split) if not window else min(-(-max(lens) // split), (window - 1) // split + 2)
             part = torch.full((len(last) * H * n_splits * k.diff_part_floats(dv),), float("nan"), dtype=torch.float32, device="cuda")
             out1 = torch.full((len(last), H * dv), float("nan"), dtype=tdt, device="cuda")
-            for rows in (16, 64):
+            for rows in ((8, 16, 64) if H // G <= 8 else (16, 64)):
                 out1.fill_(float("nan"))
                 k.diff_attention_mma(q1, k_pages, v_pages, tables, starts1, pos1, out1, H, 0.5, lam, eps, out_scale, 0, len(lens), 0,
                                      len(last), k.diff_mma_tiles([1] * len(last), H // G, rows), window=window, softcap=cap,
